@@ -1,0 +1,132 @@
+/*
+ * nq_fp8.h — C ABI of libnq_fp8.so: the FP8 (e4m3) W8A8 block-scaled linear
+ * path for NVIDIA B200 (sm_100a).
+ *
+ * This is the native boundary behind the drop-in replacements for nano_qwen's
+ * tensor-parallel linear layers.  Plain pointers and sizes only: no torch
+ * types, no C++ types.  All pointers are DEVICE pointers unless said
+ * otherwise; `stream` is a `cudaStream_t` passed as `void*` (NULL = the legacy
+ * default stream).  Every function returns an NQ_* status: 0 on success,
+ * negative on a rejected call; nothing throws, aborts or traps.  Calls only
+ * enqueue work (no host synchronisation), so they are legal inside CUDA-graph
+ * stream capture once the library has been initialised on the device
+ * (nq_init, or any earlier call).
+ *
+ * Layouts
+ *   x    [M, K]  bf16, row-major, row stride `ldx` elements
+ *   xq   [M, K]  e4m3, row-major, row stride `ld_xq` BYTES (multiple of 16)
+ *   sx   [ceil(K/128), ld_sx] fp32, K-group major: sx[g*ld_sx + m] is the
+ *        dequantisation multiplier of token m, K-group g   (ld_sx >= M)
+ *   wq   [N, K]  e4m3, row-major, row stride `ld_wq` bytes (multiple of 16)
+ *   sw   [ceil(N/128), ld_sw] fp32, row-major: sw[bn*ld_sw + bk]
+ *        (what FP8 checkpoints call `weight_scale_inv`)        (ld_sw >= ceil(K/128))
+ *   bias [N] bf16 or NULL
+ *   y    [M, N]  bf16, row-major, row stride `ldy` elements
+ *
+ * What each entry point stands in for in the reference (nano_qwen,
+ * src/nano_qwen/layers/linear.py):
+ *   nq_fp8_linear / nq_fp8_gemm_bs128   the `F.linear(x, W, b)` call of
+ *       ReplicatedLinear.forward (:50-51), ColumnParallelLinear.forward
+ *       (:72-73; inherited by MergedColumnParallelLinear and
+ *       QKVParallelLinear) and RowParallelLinear.forward (:152-153).
+ *   nq_act_quant_e4m3_g128              no counterpart: the reference keeps
+ *       activations in bf16; this is the dynamic per-token 1x128 quantiser
+ *       that feeds the FP8 GEMM.
+ *   nq_weight_quant_e4m3_b128           no counterpart: offline 128x128 block
+ *       quantiser used for random-init weights and bf16 checkpoints.
+ * The row-parallel all-reduce (linear.py:154-155) stays in the host layer
+ * (torch.distributed / NCCL).
+ */
+#ifndef NQ_FP8_H_
+#define NQ_FP8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NQ_OK 0
+#define NQ_ERR_BAD_ARGUMENT (-1)   /* null pointer, negative size, misaligned pointer or stride */
+#define NQ_ERR_UNSUPPORTED (-2)    /* shape outside what the kernels cover */
+#define NQ_ERR_WORKSPACE (-3)      /* workspace missing or smaller than nq_fp8_gemm_workspace_bytes */
+#define NQ_ERR_CUDA (-4)           /* a CUDA runtime/driver call failed (see nq_last_cuda_error) */
+#define NQ_ERR_DEVICE_TIMEOUT (-5) /* a bounded device-side wait expired (reported by nq_device_status) */
+#define NQ_ERR_NOT_SM100 (-6)      /* the current device is not compute capability 10.x */
+
+/* Algorithm selector for the GEMM (`algo` argument). */
+#define NQ_ALGO_AUTO 0
+#define NQ_ALGO_TOKEN_LANE 1  /* tokens on the 128 UMMA lanes; 128x256 tiles; prefill-sized M */
+#define NQ_ALGO_WEIGHT_LANE 2 /* weight rows on the lanes (swap-AB), split-K; decode-sized M */
+
+/* ABI version of this header (major*100 + minor). */
+int nq_version(void);
+
+/* Human-readable name of a status code (static storage, never NULL). */
+const char* nq_status_string(int status);
+
+/* Text of the last CUDA error seen by this library on the calling thread. */
+const char* nq_last_cuda_error(void);
+
+/* One-time per-device set-up (driver entry points, status block, kernel
+ * attributes) for the CURRENT device.  Implicit in every other call; call it
+ * explicitly before starting a stream capture. */
+int nq_init(void);
+
+/* Dynamic activation quantiser: bf16 [M,K] -> e4m3 [M,K] + fp32 group scales.
+ * scale = max(amax, 1e-10) / 448 (IEEE fp32 divide), q = RNE_e4m3(x / scale).
+ * A ragged last group (K % 128 != 0) takes its amax over the elements present. */
+int nq_act_quant_e4m3_g128(const void* x, int64_t M, int64_t K, int64_t ldx,
+                           void* xq, int64_t ld_xq, float* sx, int64_t ld_sx, void* stream);
+
+/* Offline weight quantiser: bf16 [N,K] -> e4m3 [N,K] + fp32 128x128 block scales,
+ * same scale/rounding rule as above. */
+int nq_weight_quant_e4m3_b128(const void* w, int64_t N, int64_t K, int64_t ldw,
+                              void* wq, int64_t ld_wq, float* sw, int64_t ld_sw, void* stream);
+
+/* Bytes of zero-initialised scratch the GEMM may need for this problem.
+ * The buffer must be zero-filled ONCE by the caller before its first use; the
+ * library leaves it in a reusable state after every launch.  Two launches that
+ * may overlap on the GPU (different streams) need different buffers. */
+size_t nq_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/* y = bf16( sum_t sx[t,m] * sw[n/128,t] * (xq[m, tile t] . wq[n, tile t]) + bias[n] ),
+ * tile = 128 consecutive k; inner products accumulate in fp32 on the tensor
+ * cores, the scaled sum over tiles in fp32 registers.
+ * `split_k` = 0 lets the library choose; otherwise it is a hint for
+ * NQ_ALGO_WEIGHT_LANE. */
+int nq_fp8_gemm_bs128(const void* xq, int64_t ld_xq, const float* sx, int64_t ld_sx,
+                      const void* wq, int64_t ld_wq, const float* sw, int64_t ld_sw,
+                      const void* bias, void* y, int64_t ldy,
+                      int64_t M, int64_t N, int64_t K,
+                      void* workspace, size_t workspace_bytes,
+                      int algo, int split_k, void* stream);
+
+/* Convenience: activation quantiser + GEMM in one call.  `xq_scratch`
+ * (M*ld_xq bytes, ld_xq = K rounded up to 16) and `sx_scratch`
+ * (ceil(K/128)*ld_sx floats, ld_sx = M rounded up to 4) are caller-owned. */
+int nq_fp8_linear(const void* x, int64_t ldx,
+                  const void* wq, int64_t ld_wq, const float* sw, int64_t ld_sw,
+                  const void* bias, void* y, int64_t ldy,
+                  int64_t M, int64_t N, int64_t K,
+                  void* xq_scratch, float* sx_scratch,
+                  void* workspace, size_t workspace_bytes,
+                  int algo, int split_k, void* stream);
+
+/* Reads the device-side status block of the current device (mapped host
+ * memory; call after synchronising the stream).  code = 0 or
+ * NQ_ERR_DEVICE_TIMEOUT, where/block/aux say which wait expired.  `reset`
+ * non-zero clears it. */
+int nq_device_status(int* code, int* where, int* block, int* aux, int reset);
+
+/* Wall-clock limit (nanoseconds) of one device-side wait; default 2e9. */
+int nq_set_wait_limit_ns(uint64_t ns);
+
+/* Number of kernels this library has launched on the calling process so far. */
+int64_t nq_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NQ_FP8_H_ */

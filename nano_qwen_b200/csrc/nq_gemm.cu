@@ -1,0 +1,696 @@
+// Block-scaled FP8 GEMM kernels for sm_100a.
+//
+//   y[m,n] = bf16( sum_t sx[t,m] * sw[n/128,t] * ( xq[m, tile t] . wq[n, tile t] ) + bias[n] )
+//
+// Both kernels share one structure: a TMA producer warp fills a ring of
+// shared-memory stages (one 128-byte-swizzled K-tile of each operand per
+// stage), one thread issues tcgen05.mma (kind::f8f6f4, e4m3 x e4m3 -> fp32)
+// into a ring of TMEM accumulators, ONE K-TILE PER ACCUMULATOR, and the
+// epilogue warps drain each accumulator with tcgen05.ld, multiply by the fp32
+// scale product of that K-tile and add into fp32 registers ("promotion").  The
+// fp32 scales cannot ride inside the MMA, hence one drain per 128-wide K-tile;
+// the TMEM ring lets the drain of tile t overlap the MMAs of tile t+1.
+//
+//   token_lane_kernel   tokens on the 128 TMEM lanes, BN weight rows on the
+//                       columns; persistent over output tiles.  One scale per
+//                       thread and K-tile.  For prefill-sized M (tensor bound).
+//   weight_lane_kernel  swap-AB: 128 weight rows on the lanes, the (few) tokens
+//                       on the columns; split-K over a thread-block cluster,
+//                       partial sums exchanged through distributed shared
+//                       memory and summed in a fixed order (deterministic, no
+//                       global scratch).  For decode-sized M (HBM bound).
+//
+// No TMA multicast anywhere (these kernels also run in multi-GPU jobs).
+#include "nq_internal.cuh"
+
+namespace nq {
+
+namespace {
+
+constexpr int kTileK = 128;          // bytes == elements per K-tile row; one swizzle atom
+constexpr int kLaneTileBytes = 128 * kTileK;
+
+// wait-site ids reported in DeviceStatus::where
+enum : int {
+  kSiteProdEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpiTmemFull = 4, kSiteTeardown = 5,
+  kSiteWeightLane = 16  // added to the above for the weight-lane kernel
+};
+
+struct __align__(8) PipeBars {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[4];
+  uint64_t tmem_empty[4];
+  uint64_t teardown;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ uint8_t* align_1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float bf16_to_float(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+// After an abort: give copies and MMAs still in flight a bounded time to land
+// before shared memory and TMEM are released.
+__device__ __noinline__ void drain_after_abort(PipeBars* bars, int stages, uint32_t issued) {
+  const uint64_t t0 = globaltimer_ns();
+  const uint32_t first = issued > static_cast<uint32_t>(stages) ? issued - stages : 0;
+  for (uint32_t i = first; i < issued; ++i) {
+    const int s = i % stages;
+    const uint32_t ph = (i / stages) & 1;
+    while (!mbar_try_wait(&bars->full[s], ph)) {
+      if (globaltimer_ns() - t0 > 20000000ull) return;   // 20 ms in total
+    }
+  }
+}
+
+}  // namespace
+
+// =========================================================================== //
+//                            token-lane kernel                                //
+// =========================================================================== //
+template <int BN>
+struct TokenLane {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStageBytes = kLaneTileBytes + BN * kTileK;
+  static constexpr int kEpiWarps = 8;
+  static constexpr int kFirstEpiWarp = 4;           // warps 0..3: producer, MMA issuer, two idle (one warpgroup)
+  static constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
+  static constexpr int kCols = BN / 2;              // accumulator columns per epilogue thread
+  static constexpr int kNumAcc = 2;
+  static constexpr int kTmemCols = kNumAcc * BN;    // 512 or 256
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 1024;
+  static constexpr int kGroupM = 16;                // M-tiles per rasterisation group
+};
+
+struct TokenLaneParams {
+  const float* sx; int64_t ld_sx;
+  const float* sw; int64_t ld_sw;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y; int64_t ldy;
+  int M, N, K;
+  int y_vec;                  // 1: 16-byte stores are legal for y
+  DeviceStatus* status;
+  uint64_t wait_limit_ns;
+};
+
+template <int BN>
+__device__ __forceinline__ void token_lane_tile_coords(int tile, int num_m, int num_n, int& m_t, int& n_t) {
+  constexpr int G = TokenLane<BN>::kGroupM;
+  const int per_group = G * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * G;
+  const int gsize = min(num_m - first_m, G);
+  const int r = tile - group * per_group;
+  m_t = first_m + r % gsize;
+  n_t = r / gsize;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(TokenLane<BN>::kThreads, 1)
+token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                  const TokenLaneParams p) {
+  using C = TokenLane<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align_1024(smem_raw);
+  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kStages * C::kStageBytes);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int b = 0; b < C::kNumAcc; ++b) { mbar_init(&bars->tmem_full[b], 1); mbar_init(&bars->tmem_empty[b], C::kEpiWarps); }
+    mbar_init(&bars->teardown, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_w);
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, C::kTmemCols); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns};
+
+  pdl_launch_next();
+  pdl_wait_prior();   // xq / sx come from the preceding quantiser launch
+
+  const int num_m = (p.M + 127) / 128;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int KT = (p.K + kTileK - 1) / kTileK;
+  uint32_t issued = 0;
+
+  // The epilogue holds BN/2 fp32 accumulators per thread: move registers from
+  // the producer/MMA warpgroup to the two epilogue warpgroups.
+  if (warp < C::kFirstEpiWarp) {
+   setmaxnreg_dec<64>();
+   if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        int m_t, n_t;
+        token_lane_tile_coords<BN>(tile, num_m, num_n, m_t, n_t);
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteProdEmpty, kt)) { ok = false; break; }
+          uint8_t* a = smem + s * C::kStageBytes;
+          mbar_arrive_expect_tx(&bars->full[s], C::kStageBytes);
+          tma_load_2d(a, &tm_x, &bars->full[s], kt * kTileK, m_t * 128);
+          tma_load_2d(a + kLaneTileBytes, &tm_w, &bars->full[s], kt * kTileK, n_t * BN);
+        }
+      }
+      issued = it;
+      if (!ok) drain_after_abort(bars, C::kStages, issued);
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_e4m3_f32(128, BN);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const int b = it % C::kNumAcc;
+          const uint32_t aph = (it / C::kNumAcc) & 1;
+          if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          if (!mbar_wait(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
+          const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
+          const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
+          const uint32_t d = tmem_base + b * BN;
+#pragma unroll
+          for (int k = 0; k < kTileK / 32; ++k)   // 32 bytes of K per UMMA: +2 in the (addr >> 4) field
+            umma_f8(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+          umma_commit(&bars->empty[s]);
+          umma_commit(&bars->tmem_full[b]);
+        }
+      }
+      if (!ok) {   // let MMAs already issued finish before TMEM is freed
+        umma_commit(&bars->teardown);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bars->teardown, 0) && globaltimer_ns() - t0 < 20000000ull) {}
+      }
+    }
+   }
+  } else {
+    setmaxnreg_inc<216>();
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int h = (warp - C::kFirstEpiWarp) >> 2;   // which half of the BN columns
+    const int row = q * 32 + lane;
+    float acc[C::kCols];
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      int m_t, n_t;
+      token_lane_tile_coords<BN>(tile, num_m, num_n, m_t, n_t);
+      const int m = m_t * 128 + row;
+      const int n_base = n_t * BN + h * C::kCols;
+      const bool live = (m < p.M) && (n_base < p.N);
+      const float* sx_col = p.sx + m;
+      const float* sw_row = p.sw + static_cast<int64_t>(n_base >> 7) * p.ld_sw;
+#pragma unroll
+      for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
+      float s_next = live ? __ldg(sx_col) * __ldg(sw_row) : 0.0f;
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        const float s = s_next;
+        if (kt + 1 < KT && live) s_next = __ldg(sx_col + static_cast<int64_t>(kt + 1) * p.ld_sx) * __ldg(sw_row + kt + 1);
+        const int b = it % C::kNumAcc;
+        const uint32_t aph = (it / C::kNumAcc) & 1;
+        if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * BN + h * C::kCols;
+#pragma unroll
+        for (int c = 0; c < C::kCols / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (c == C::kCols / 32 - 1) {   // accumulator fully read: hand it back to the MMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), s, acc[c * 32 + i]);
+        }
+      }
+      if (!ok) break;
+      // ---- write the tile: this thread owns row m, kCols consecutive columns ----
+      if (m < p.M) {
+        __nv_bfloat16* yrow = p.y + static_cast<int64_t>(m) * p.ldy;
+#pragma unroll
+        for (int j = 0; j < C::kCols; j += 8) {
+          const int n = n_base + j;
+          if (n >= p.N) break;
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = acc[j + i];
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
+          }
+          if (p.y_vec && n + 8 <= p.N) {
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(yrow + n) = o;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (n + i < p.N) yrow[n + i] = __float2bfloat16_rn(v[i]);
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// =========================================================================== //
+//                            weight-lane kernel                               //
+// =========================================================================== //
+template <int TOK>
+struct WeightLane {
+  static constexpr int kStages = (TOK == 32) ? 5 : (TOK == 64) ? 4 : (TOK == 128) ? 6 : 4;
+  static constexpr int kStageBytes = kLaneTileBytes + TOK * kTileK;
+  static constexpr int kEpiWarps = (TOK == 256) ? 8 : 4;
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static constexpr int kCols = TOK / (kEpiWarps / 4);     // accumulator columns per epilogue thread
+  static constexpr int kNumAcc = (TOK == 256) ? 2 : 4;
+  static constexpr int kTmemCols = (kNumAcc * TOK) < 32 ? 32 : (kNumAcc * TOK);
+  static constexpr int kExchangeBytes = 128 * TOK * 4;    // fp32 partial tile, [token][weight row]
+  static constexpr int kPipeBytes = kStages * kStageBytes;
+  static_assert(kExchangeBytes <= kPipeBytes, "partial tile must fit in the drained pipeline stages");
+  static constexpr int kSmemBytes = 1024 + kPipeBytes + 2 * TOK * 4 + 1024;
+};
+
+struct WeightLaneParams {
+  const float* sx; int64_t ld_sx;
+  const float* sw; int64_t ld_sw;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y; int64_t ldy;
+  int M, N, K;
+  int splits;                 // == cluster size along grid y
+  int tok_box;                // token rows per TMA box of xq (what one stage receives)
+  int y_vec;                  // 1: 8-byte stores are legal for y
+  DeviceStatus* status;
+  uint64_t wait_limit_ns;
+};
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_smem_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void epi_bar_sync(int nthreads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+}
+
+// grid = (ceil(N/128), splits, ceil(M/TOK)), cluster = (1, splits, 1).
+template <int TOK>
+__global__ void __launch_bounds__(WeightLane<TOK>::kThreads)
+weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                   const WeightLaneParams p) {
+  using C = WeightLane<TOK>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align_1024(smem_raw);
+  float* sc = reinterpret_cast<float*>(smem + C::kPipeBytes);             // [2][TOK] scale products
+  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kPipeBytes + 2 * TOK * 4);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int n_t = blockIdx.x;
+  const int z = blockIdx.y;
+  const int m0 = blockIdx.z * TOK;
+  const int m_count = min(p.M - m0, TOK);
+  const int n_umma = (m_count + 15) & ~15;                // tokens padded to the UMMA N granularity
+  const int KT = (p.K + kTileK - 1) / kTileK;
+  const int kt0 = static_cast<int>((static_cast<int64_t>(z) * KT) / p.splits);
+  const int kt1 = static_cast<int>((static_cast<int64_t>(z + 1) * KT) / p.splits);
+  const int nkt = kt1 - kt0;
+  const uint32_t stage_tx = kLaneTileBytes + p.tok_box * kTileK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int b = 0; b < C::kNumAcc; ++b) { mbar_init(&bars->tmem_full[b], 1); mbar_init(&bars->tmem_empty[b], C::kEpiWarps); }
+    mbar_init(&bars->teardown, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_x);
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, C::kTmemCols); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns};
+  pdl_launch_next();
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    // Weights never depend on the preceding launch: their first stages are in
+    // flight before the dependency wait; activations follow after it.
+    if (lane == 0) {
+      const uint64_t stream_once = l2_policy_evict_first();
+      const int pre = min(nkt, C::kStages);
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* a = smem + i * C::kStageBytes;
+        mbar_arrive_expect_tx(&bars->full[i], stage_tx);
+        tma_load_2d_hint(a, &tm_w, &bars->full[i], (kt0 + i) * kTileK, n_t * 128, stream_once);
+      }
+      pdl_wait_prior();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * C::kStageBytes + kLaneTileBytes, &tm_x, &bars->full[i], (kt0 + i) * kTileK, m0);
+      bool ok = true;
+      int i = pre;
+      for (; i < nkt; ++i) {
+        const int s = i % C::kStages;
+        const uint32_t ph = (i / C::kStages) & 1;
+        if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteWeightLane + kSiteProdEmpty, i)) { ok = false; break; }
+        uint8_t* a = smem + s * C::kStageBytes;
+        mbar_arrive_expect_tx(&bars->full[s], stage_tx);
+        tma_load_2d_hint(a, &tm_w, &bars->full[s], (kt0 + i) * kTileK, n_t * 128, stream_once);
+        tma_load_2d(a + kLaneTileBytes, &tm_x, &bars->full[s], (kt0 + i) * kTileK, m0);
+      }
+      if (!ok) drain_after_abort(bars, C::kStages, static_cast<uint32_t>(i));
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_e4m3_f32(128, n_umma);
+      bool ok = true;
+      for (int i = 0; i < nkt; ++i) {
+        const int b = i % C::kNumAcc;
+        const uint32_t aph = (i / C::kNumAcc) & 1;
+        if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteWeightLane + kSiteMmaTmemEmpty, i)) { ok = false; break; }
+        const int s = i % C::kStages;
+        const uint32_t ph = (i / C::kStages) & 1;
+        if (!mbar_wait(&bars->full[s], ph, ac, kSiteWeightLane + kSiteMmaFull, i)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
+        const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
+        const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
+        const uint32_t d = tmem_base + b * TOK;
+#pragma unroll
+        for (int k = 0; k < kTileK / 32; ++k)
+          umma_f8(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+        umma_commit(&bars->empty[s]);
+        umma_commit(&bars->tmem_full[b]);
+      }
+      if (!ok) {
+        umma_commit(&bars->teardown);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bars->teardown, 0) && globaltimer_ns() - t0 < 20000000ull) {}
+      }
+    }
+  }
+
+  float acc[C::kCols];
+  const int q = warp & 3;
+  const int h = (warp >= 2) ? ((warp - 2) >> 2) : 0;       // column half (TOK == 256 only)
+  const int col0 = h * C::kCols;
+  bool epi_ok = true;
+  if (warp >= 2) {
+    // ------------------------------ epilogue ----------------------------------
+    pdl_wait_prior();                                       // sx comes from the quantiser launch
+    constexpr int kEpiThreads = 32 * C::kEpiWarps;
+    const int et = threadIdx.x - 64;                        // 0 .. kEpiThreads-1
+    const float* sw_row = p.sw + static_cast<int64_t>(n_t) * p.ld_sw;
+    const bool has_col = (et < TOK) && (m0 + et < p.M);
+#pragma unroll
+    for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
+    float s_next = 0.0f;
+    if (nkt > 0 && et < TOK)
+      s_next = has_col ? __ldg(p.sx + static_cast<int64_t>(kt0) * p.ld_sx + m0 + et) * __ldg(sw_row + kt0) : 0.0f;
+    for (int i = 0; i < nkt; ++i) {
+      const float s_mine = s_next;
+      if (i + 1 < nkt && has_col)
+        s_next = __ldg(p.sx + static_cast<int64_t>(kt0 + i + 1) * p.ld_sx + m0 + et) * __ldg(sw_row + kt0 + i + 1);
+      float* scb = sc + (i & 1) * TOK;
+      if (et < TOK) scb[et] = s_mine;
+      const int b = i % C::kNumAcc;
+      const uint32_t aph = (i / C::kNumAcc) & 1;
+      if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteWeightLane + kSiteEpiTmemFull, i)) { epi_ok = false; }
+      // every epilogue thread reaches this barrier, also when aborting
+      epi_bar_sync(kEpiThreads);
+      if (!epi_ok || bars->abort_flag) { epi_ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * TOK + col0;
+#pragma unroll
+      for (int c = 0; c < C::kCols / 16; ++c) {
+        if (col0 + c * 16 < n_umma) {
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + c * 16, r);
+          tmem_ld_wait();
+          const float4* s4 = reinterpret_cast<const float4*>(scb + col0 + c * 16);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 sv = s4[j];
+            acc[c * 16 + 4 * j + 0] = fmaf(__uint_as_float(r[4 * j + 0]), sv.x, acc[c * 16 + 4 * j + 0]);
+            acc[c * 16 + 4 * j + 1] = fmaf(__uint_as_float(r[4 * j + 1]), sv.y, acc[c * 16 + 4 * j + 1]);
+            acc[c * 16 + 4 * j + 2] = fmaf(__uint_as_float(r[4 * j + 2]), sv.z, acc[c * 16 + 4 * j + 2]);
+            acc[c * 16 + 4 * j + 3] = fmaf(__uint_as_float(r[4 * j + 3]), sv.w, acc[c * 16 + 4 * j + 3]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+    }
+  }
+
+  // All MMAs of this CTA have completed (the epilogue waited for the last
+  // accumulator), so the pipeline stages are free: reuse them for the exchange.
+  __syncthreads();
+  float* xch = reinterpret_cast<float*>(smem);              // [TOK][128] fp32, weight row fastest
+  if (warp >= 2) {
+    const int nrow = q * 32 + lane;
+#pragma unroll
+    for (int c = 0; c < C::kCols; ++c)
+      if (col0 + c < n_umma) xch[(col0 + c) * 128 + nrow] = epi_ok ? acc[c] : 0.0f;
+  }
+  cluster_sync_all();   // partial tiles of all splits are visible cluster-wide
+
+  if (warp >= 2 && bars->abort_flag == 0) {
+    // This CTA sums tokens z, z+splits, ... over all splits in rank order (fixed
+    // order => bit-identical results run to run), adds the bias and writes y.
+    const uint32_t my_rank = cluster_ctarank();
+    const int et = threadIdx.x - 64;
+    const int nq4 = et & 31;                               // which 4 weight rows
+    const int n = n_t * 128 + nq4 * 4;
+    for (int mi = static_cast<int>(my_rank) + (et >> 5) * p.splits; mi < m_count; mi += p.splits * C::kEpiWarps) {
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      const uint32_t local = smem_u32(xch + mi * 128 + nq4 * 4);
+      for (int r = 0; r < p.splits; ++r) {
+        const float4 v = ld_dsmem_f4(local, static_cast<uint32_t>(r));
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+      }
+      if (n < p.N) {
+        float v[4] = {sum.x, sum.y, sum.z, sum.w};
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
+        }
+        __nv_bfloat16* yp = p.y + static_cast<int64_t>(m0 + mi) * p.ldy + n;
+        if (p.y_vec && n + 4 <= p.N) {
+          uint2 o;
+          o.x = pack_bf16x2(v[0], v[1]);
+          o.y = pack_bf16x2(v[2], v[3]);
+          *reinterpret_cast<uint2*>(yp) = o;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (n + i < p.N) yp[i] = __float2bfloat16_rn(v[i]);
+        }
+      }
+    }
+  }
+  cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// =========================================================================== //
+//                                launchers                                     //
+// =========================================================================== //
+namespace {
+
+template <typename Kern, typename... Args>
+cudaError_t launch_ex(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_y, bool pdl,
+                      Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (cluster_y > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = static_cast<unsigned>(cluster_y);
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+template <int BN>
+int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
+  using C = TokenLane<BN>;
+  CUtensorMap tm_x, tm_w;
+  int st = make_tmap_u8_2d(&tm_x, a.xq, a.M, a.K, a.ld_xq, 128);
+  if (st != NQ_OK) return st;
+  st = make_tmap_u8_2d(&tm_w, a.wq, a.N, a.K, a.ld_wq, BN);
+  if (st != NQ_OK) return st;
+  TokenLaneParams p;
+  p.sx = a.sx; p.ld_sx = a.ld_sx; p.sw = a.sw; p.ld_sw = a.ld_sw;
+  p.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
+  p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
+  p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
+  p.status = ctx->status_dev;
+  p.wait_limit_ns = wait_limit_ns();
+  const int64_t tiles = ((a.M + 127) / 128) * ((a.N + BN - 1) / BN);
+  const int grid = static_cast<int>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  cudaError_t e = launch_ex(token_lane_kernel<BN>, dim3(grid), dim3(C::kThreads), C::kSmemBytes, a.stream, 1, a.pdl,
+                            tm_x, tm_w, p);
+  count_launch();
+  return check_cuda(e);
+}
+
+template <int TOK>
+int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
+  using C = WeightLane<TOK>;
+  const int tokens_box = static_cast<int>(a.M >= TOK ? TOK : ((a.M + 15) / 16) * 16);
+  CUtensorMap tm_x, tm_w;
+  int st = make_tmap_u8_2d(&tm_w, a.wq, a.N, a.K, a.ld_wq, 128);
+  if (st != NQ_OK) return st;
+  st = make_tmap_u8_2d(&tm_x, a.xq, a.M, a.K, a.ld_xq, tokens_box);
+  if (st != NQ_OK) return st;
+  WeightLaneParams p;
+  p.sx = a.sx; p.ld_sx = a.ld_sx; p.sw = a.sw; p.ld_sw = a.ld_sw;
+  p.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
+  p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
+  p.splits = splits;
+  p.tok_box = tokens_box;
+  p.y_vec = (a.ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 8 == 0);
+  p.status = ctx->status_dev;
+  p.wait_limit_ns = wait_limit_ns();
+  dim3 grid(static_cast<unsigned>((a.N + 127) / 128), static_cast<unsigned>(splits),
+            static_cast<unsigned>((a.M + TOK - 1) / TOK));
+  cudaError_t e = launch_ex(weight_lane_kernel<TOK>, grid, dim3(C::kThreads), C::kSmemBytes, a.stream, splits, a.pdl,
+                            tm_w, tm_x, p);
+  count_launch();
+  return check_cuda(e);
+}
+
+}  // namespace
+
+int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
+  // 128-wide tiles when the 256-wide grid would leave most SMs idle.
+  const int64_t tiles256 = ((a.M + 127) / 128) * ((a.N + 255) / 256);
+  if (a.N <= 128 || tiles256 * 2 <= ctx->sm_count) return run_token_lane<128>(a, ctx);
+  return run_token_lane<256>(a, ctx);
+}
+
+int weight_lane_pick_split(int64_t M, int64_t N, int64_t K, int sm_count) {
+  const int64_t KT = (K + 127) / 128;
+  const int64_t n_tiles = (N + 127) / 128;
+  const int64_t m_tiles = M <= 256 ? 1 : (M + 255) / 256;
+  // aim for about two CTAs per SM, at least two K-tiles per CTA, cluster size <= 8
+  int best = 1;
+  for (int s = 1; s <= 8; s *= 2) {
+    if (KT / s < 2 && s > 1) break;
+    best = s;
+    if (n_tiles * m_tiles * s >= 2 * static_cast<int64_t>(sm_count)) break;
+  }
+  return best;
+}
+
+size_t weight_lane_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
+
+int launch_gemm_weight_lane(const GemmArgs& a, DeviceCtx* ctx) {
+  int splits = a.split_k;
+  if (splits <= 0) splits = weight_lane_pick_split(a.M, a.N, a.K, ctx->sm_count);
+  const int64_t KT = (a.K + 127) / 128;
+  if (splits > 8) splits = 8;
+  while (splits > 1 && splits > KT) splits >>= 1;
+  if (splits & (splits - 1)) {   // round down to a power of two (cluster shapes 1,2,4,8)
+    int s = 1;
+    while (s * 2 <= splits) s *= 2;
+    splits = s;
+  }
+  if (a.M <= 32) return run_weight_lane<32>(a, ctx, splits);
+  if (a.M <= 64) return run_weight_lane<64>(a, ctx, splits);
+  if (a.M <= 128) return run_weight_lane<128>(a, ctx, splits);
+  return run_weight_lane<256>(a, ctx, splits);
+}
+
+int setup_gemm_kernels() {
+  cudaError_t e;
+#define NQ_SET_SMEM(kern, bytes)                                                                  \
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);             \
+  if (e != cudaSuccess) return check_cuda(e);
+  NQ_SET_SMEM(token_lane_kernel<128>, TokenLane<128>::kSmemBytes)
+  NQ_SET_SMEM(token_lane_kernel<256>, TokenLane<256>::kSmemBytes)
+  NQ_SET_SMEM(weight_lane_kernel<32>, WeightLane<32>::kSmemBytes)
+  NQ_SET_SMEM(weight_lane_kernel<64>, WeightLane<64>::kSmemBytes)
+  NQ_SET_SMEM(weight_lane_kernel<128>, WeightLane<128>::kSmemBytes)
+  NQ_SET_SMEM(weight_lane_kernel<256>, WeightLane<256>::kSmemBytes)
+#undef NQ_SET_SMEM
+  return NQ_OK;
+}
+
+}  // namespace nq
