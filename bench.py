@@ -1,0 +1,386 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 W8A8 linear stack (the tensor-parallel linear layers of nano_qwen).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Workload (one "step"): the full 36-layer Qwen3-8B-shaped linear stack — per layer
+QKVParallelLinear 4096->6144, RowParallelLinear (o_proj) 4096->4096,
+MergedColumnParallelLinear (gate_up) 4096->24576, RowParallelLinear (down)
+12288->4096 — run once as a batched-decode pass (M = 256 tokens, replayed from a
+CUDA graph, as the model runner does for decode) and once as a chunked-prefill
+pass (M = 8192 tokens, eager), tensor-parallel over the N ranks (column layers
+sharded on N, row layers on K with a bf16 all-reduce).  Random-init weights
+(bf16 N(0, 0.02) quantised to e4m3 with 128x128 block scales), N(0,1)
+activations quantised dynamically inside the timed region, synthetic data.
+Each linear reads its own activation matrix (layers are not chained through
+attention / SiLU, which are outside this path).
+
+One JSON line is printed by rank 0; see the keys at the bottom of main().
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, LAYERS = 4096, 32, 8, 128, 12288, 36
+M_DECODE, M_PREFILL = 256, 8192
+# 2 * sum(N*K) over the four linears of one layer
+FLOPS_PER_TOKEN_LAYER = 2 * (HIDDEN * (HEADS + 2 * KV_HEADS) * HEAD_DIM + HIDDEN * HIDDEN + HIDDEN * 2 * INTER + INTER * HIDDEN)
+KINDS = ("qkv", "o_proj", "gate_up", "down")
+
+
+def flops_per_step() -> float:
+    return float(LAYERS) * FLOPS_PER_TOKEN_LAYER * (M_DECODE + M_PREFILL)
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- #
+# CPU arm: the oracle (port of the reference path) timed on the host cores     #
+# --------------------------------------------------------------------------- #
+def cpu_reference_sample(repeats: int, m_decode: int = 256, m_prefill: int = 1024) -> dict:
+    """Times ONE layer of the stack on the CPU: dynamic activation quantisation, dequantisation of
+    both operands to fp32 and the reference's ``F.linear`` (fp32), bf16 out — for a decode pass of
+    ``m_decode`` tokens and a prefill chunk of ``m_prefill`` tokens.  Returns TFLOP/s."""
+    from oracle import fp8_spec as S, ref_linear as R
+    torch.manual_seed(0)
+    shapes = {"qkv": (HIDDEN, (HEADS + 2 * KV_HEADS) * HEAD_DIM), "o_proj": (HIDDEN, HIDDEN),
+              "gate_up": (HIDDEN, 2 * INTER), "down": (INTER, HIDDEN)}
+    weights = {}
+    for name, (k, n) in shapes.items():
+        w = (torch.randn(n, k) * 0.02).to(torch.bfloat16)
+        weights[name] = S.quantize_weight_block128(w)
+    acts = {(name, m): torch.randn(m, shapes[name][0]).to(torch.bfloat16)
+            for name in shapes for m in (m_decode, m_prefill)}
+
+    def one_pass(m):
+        for name in KINDS:
+            wq, sw = weights[name]
+            xq, sx = S.quantize_act_group128(acts[(name, m)])
+            R.column_forward(S.dequantize_act(xq, sx), S.dequantize_weight(wq, sw)).to(torch.bfloat16)
+
+    one_pass(m_decode)          # warm-up (thread pool, allocator)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        one_pass(m_decode)
+        one_pass(m_prefill)
+        times.append(time.perf_counter() - t0)
+    flops = FLOPS_PER_TOKEN_LAYER * (m_decode + m_prefill)
+    best = min(times)
+    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"1 of {LAYERS} layers, decode M={m_decode} + prefill chunk M={m_prefill} "
+                      f"(act quant + dequant + fp32 F.linear), best of {repeats}, {best:.2f} s",
+            "seconds": best, "host_cpus": os.cpu_count()}
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_reference_sample(1, 64, 64)
+    t0 = time.perf_counter()
+    res = cpu_reference_sample(steps)
+    wall = time.perf_counter() - t0
+    line = {
+        "impl": "reference", "metric": "fp8_linear_stack_tflops", "value": res["value"], "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": res["seconds"] * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "Qwen3-8B-shaped 36-layer FP8 linear stack, decode M=256 + prefill M=8192 per step "
+                               "(CPU arm: bounded sample, see cpu_baseline.sample)", "tp": args.gpus},
+        "cpu_baseline": res,
+        "e2e": {"value": res["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": wall,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- #
+# GPU arm                                                                      #
+# --------------------------------------------------------------------------- #
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait()
+        sm, mx, reasons, power = [], [], set(), []
+        for row in open(self.path):
+            f = [c.strip() for c in row.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # samples taken under load: the upper half by power draw
+        order = sorted(range(len(sm)), key=lambda i: power[i])
+        hot = [sm[i] for i in order[len(order) // 2:]]
+        hot.sort()
+        return {"sm_mhz": hot[len(hot) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "power_w_max": max(power), "samples": len(sm)}
+
+
+def build_stack(L, ops, tp_rank: int, tp_size: int):
+    """36 x 4 drop-in layers on the current device with random-init FP8 weights (this rank's shards)."""
+    torch.set_default_device("cuda")
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        layers = []
+        for li in range(LAYERS):
+            layer = {
+                "qkv": L.QKVParallelLinear(HIDDEN, HEAD_DIM, HEADS, KV_HEADS),
+                "o_proj": L.RowParallelLinear(HIDDEN, HIDDEN),
+                "gate_up": L.MergedColumnParallelLinear(HIDDEN, [INTER, INTER]),
+                "down": L.RowParallelLinear(INTER, HIDDEN),
+            }
+            for ki, (name, mod) in enumerate(layer.items()):
+                gen = torch.Generator(device="cuda").manual_seed(1000 * li + 10 * ki + tp_rank)
+                n, k = mod.weight.shape
+                w = (torch.randn(n, k, generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                wq, sw = ops.weight_quant(w)          # this rank's shard, quantised on the device
+                mod.weight.data.copy_(wq)
+                mod.weight_scale_inv.data.copy_(sw)
+                del w, wq, sw
+            layers.append(layer)
+    finally:
+        torch.set_default_device("cpu")
+        torch.set_default_dtype(torch.float32)
+    return layers
+
+
+def input_shapes(m: int, tp: int) -> dict:
+    return {"qkv": (m, HIDDEN), "o_proj": (m, HIDDEN // tp), "gate_up": (m, HIDDEN), "down": (m, INTER // tp)}
+
+
+def run_pass(layers, xs):
+    y = None
+    for layer in layers:
+        for name in KINDS:
+            y = layer[name](xs[name])
+    return y
+
+
+def run_gpu_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("for --gpus N > 1 launch with torch.distributed.run --nproc-per-node N")
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29517")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+
+    from nano_qwen_b200 import _cabi, ops
+    from nano_qwen_b200.layers import linear as L
+    ops.init()
+    tp = world
+    layers = build_stack(L, ops, rank, tp)
+    torch.cuda.synchronize()
+
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    host = {}
+    for tag, m in (("decode", M_DECODE), ("prefill", M_PREFILL)):
+        host[tag] = {name: torch.randn(shape, generator=gen, dtype=torch.float32).to(torch.bfloat16).pin_memory()
+                     for name, shape in input_shapes(m, tp).items()}
+    dev = {tag: {name: t.cuda() for name, t in d.items()} for tag, d in host.items()}
+    out_host = {tag: torch.empty((m, HIDDEN), dtype=torch.bfloat16).pin_memory()
+                for tag, m in (("decode", M_DECODE), ("prefill", M_PREFILL))}
+
+    # decode pass: captured once, replayed every step (static input buffers, like the model runner's graph_vars)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run_pass(layers, dev["decode"])
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_decode = run_pass(layers, dev["decode"])
+
+    def step_resident():
+        graph.replay()
+        return run_pass(layers, dev["prefill"])
+
+    def step_e2e():
+        for name, t in host["decode"].items():
+            dev["decode"][name].copy_(t, non_blocking=True)
+        graph.replay()
+        out_host["decode"].copy_(y_decode, non_blocking=True)
+        xs = {name: t.cuda(non_blocking=True) for name, t in host["prefill"].items()}
+        y = run_pass(layers, xs)
+        out_host["prefill"].copy_(y, non_blocking=True)
+        return y
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0 = ops.launch_count()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() / steps, ops.launch_count() - n0
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_step, launches = timed(step_resident, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, _ = timed(step_e2e, max(1, min(args.steps, 5)), 1)
+
+    # ---- per-pass and per-kernel timings that explain the headline (same device, after the timed region) ----
+    ms_decode, _ = timed(graph.replay, 5, 2)
+    ms_prefill, _ = timed(lambda: run_pass(layers, dev["prefill"]), 3, 1)
+    # dominant kernel: the token-lane GEMM of the prefill pass, timed alone on pre-quantised activations
+    pre = {name: ops.act_quant(dev["prefill"][name]) for name in KINDS}
+
+    def prefill_gemms_only():
+        for layer in layers:
+            for name in KINDS:
+                mod = layer[name]
+                ops.fp8_gemm(pre[name][0], pre[name][1], mod.weight, mod.weight_scale_inv)
+
+    ms_gemm, n_gemm = timed(prefill_gemms_only, 3, 1)
+    n_gemm //= 3
+    dec_pre = {name: ops.act_quant(dev["decode"][name]) for name in KINDS}
+    g2 = torch.cuda.CUDAGraph()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for layer in layers:
+            for name in KINDS:
+                ops.fp8_gemm(dec_pre[name][0], dec_pre[name][1], layer[name].weight, layer[name].weight_scale_inv)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(g2):
+        for layer in layers:
+            for name in KINDS:
+                ops.fp8_gemm(dec_pre[name][0], dec_pre[name][1], layer[name].weight, layer[name].weight_scale_inv)
+    ms_dec_gemm, _ = timed(g2.replay, 5, 2)
+    torch.cuda.synchronize()
+    status = _cabi.device_status()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        flops = flops_per_step()
+        tflops = flops / (ms_step * 1e-3) / 1e12
+        prefill_flops = LAYERS * FLOPS_PER_TOKEN_LAYER * M_PREFILL / tp      # per GPU
+        kernel_tflops = prefill_flops / (ms_gemm * 1e-3) / 1e12
+        fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+        # decode: algorithmic bytes of one rank's layer = weights + scales + bf16 in/out of the four linears
+        shapes = {"qkv": (HIDDEN, (HEADS + 2 * KV_HEADS) * HEAD_DIM // tp), "o_proj": (HIDDEN // tp, HIDDEN),
+                  "gate_up": (HIDDEN, 2 * INTER // tp), "down": (INTER // tp, HIDDEN)}
+        layer_bytes = sum(2 * M_DECODE * k + n * k + 4 * ((n + 127) // 128) * ((k + 127) // 128) + 2 * M_DECODE * n
+                          for k, n in shapes.values())
+        decode_gbs = LAYERS * layer_bytes / (ms_decode * 1e-3) / 1e9
+        in_bytes = sum(t.numel() * 2 for d in host.values() for t in d.values())
+        out_bytes = sum(t.numel() * 2 for t in out_host.values())
+        cpu = cpu_reference_sample(2) if world == 1 else None
+        line = {
+            "metric": "fp8_linear_stack_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)",
+            "data": "synthetic",
+            "config": {"workload": "Qwen3-8B-shaped 36-layer FP8 linear stack: decode pass M=256 (CUDA graph) + "
+                                   "chunked-prefill pass M=8192 per step", "tp": tp, "layers": LAYERS,
+                       "l2": "weights of the stack (6.95 GB / tp) exceed L2; no flush needed"},
+            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "token_lane_kernel (prefill-pass FP8 GEMM)",
+                         "achieved": kernel_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
+                         "frac": kernel_tflops / fp8_peak,
+                         "peak_note": f"2 x bf16_tflops_sustained of {peaks['source']} (the e4m3 UMMA rate is twice the "
+                                      "bf16 rate); torch._scaled_mm per-tensor FP8 measured 3046 burst / 2618 sustained here",
+                         "launches": n_gemm, "avg_launch_us": ms_gemm * 1e3 / max(n_gemm, 1),
+                         "traffic": None},
+            "passes": {"decode_ms": ms_decode, "prefill_ms": ms_prefill, "prefill_gemm_only_ms": ms_gemm,
+                       "decode_gemm_only_ms": ms_dec_gemm,
+                       "decode_layer_us": ms_decode * 1e3 / LAYERS, "prefill_layer_us": ms_prefill * 1e3 / LAYERS,
+                       "decode_hbm_gbs": decode_gbs, "decode_hbm_frac_of_measured": decode_gbs / peaks["hbm_gbs"],
+                       "prefill_tflops": LAYERS * FLOPS_PER_TOKEN_LAYER * M_PREFILL / (ms_prefill * 1e-3) / 1e12},
+            "device_status": status["code"],
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (the product has no CPU fallback); "
+                             "use --impl reference for the CPU arm")
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

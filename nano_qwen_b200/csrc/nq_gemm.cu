@@ -21,6 +21,7 @@
 //                       global scratch).  For decode-sized M (HBM bound).
 //
 // No TMA multicast anywhere (these kernels also run in multi-GPU jobs).
+#include <cstdlib>
 #include "nq_internal.cuh"
 
 namespace nq {
@@ -97,6 +98,7 @@ struct TokenLaneParams {
   __nv_bfloat16* y; int64_t ldy;
   int M, N, K;
   int y_vec;                  // 1: 16-byte stores are legal for y
+  int debug;                  // experiments only: 1 = epilogue skips TMEM loads, 2 = loads but no FMA
   DeviceStatus* status;
   uint64_t wait_limit_ns;
 };
@@ -166,6 +168,16 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           const uint32_t ph = (it / C::kStages) & 1;
           if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteProdEmpty, kt)) { ok = false; break; }
           uint8_t* a = smem + s * C::kStageBytes;
+          if (p.debug == 4 && it >= C::kStages) {          // experiments: A only (16 KB per K-tile)
+            mbar_arrive_expect_tx(&bars->full[s], kLaneTileBytes);
+            tma_load_2d(a, &tm_x, &bars->full[s], kt * kTileK, m_t * 128);
+            continue;
+          }
+          if (p.debug == 5 && it >= C::kStages) {          // experiments: B only (32 KB per K-tile)
+            mbar_arrive_expect_tx(&bars->full[s], BN * kTileK);
+            tma_load_2d(a + kLaneTileBytes, &tm_w, &bars->full[s], kt * kTileK, n_t * BN);
+            continue;
+          }
           mbar_arrive_expect_tx(&bars->full[s], C::kStageBytes);
           tma_load_2d(a, &tm_x, &bars->full[s], kt * kTileK, m_t * 128);
           tma_load_2d(a + kLaneTileBytes, &tm_w, &bars->full[s], kt * kTileK, n_t * BN);
@@ -184,7 +196,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int b = it % C::kNumAcc;
           const uint32_t aph = (it / C::kNumAcc) & 1;
-          if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
+          if (p.debug != 3 && p.debug != 6 && !mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
           if (!mbar_wait(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
@@ -193,6 +205,14 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
           const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
           const uint32_t d = tmem_base + b * BN;
+          if (p.debug == 6 && BN == 256) {
+            constexpr uint32_t idesc_half = umma_idesc_e4m3_f32(128, 128);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+              for (int k = 0; k < kTileK / 32; ++k)
+                umma_f8(d + hh * 128, a_desc + 2 * k, b_desc + hh * 1024 + 2 * k, idesc_half, k > 0 ? 1u : 0u);
+          } else
 #pragma unroll
           for (int k = 0; k < kTileK / 32; ++k)   // 32 bytes of K per UMMA: +2 in the (addr >> 4) field
             umma_f8(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
@@ -226,15 +246,32 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       const float* sw_row = p.sw + static_cast<int64_t>(n_base >> 7) * p.ld_sw;
 #pragma unroll
       for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
-      float s_next = live ? __ldg(sx_col) * __ldg(sw_row) : 0.0f;
+      // Scale factors are fetched two K-tiles ahead and multiplied only when used,
+      // so their L2 latency never sits between two accumulator drains.
+      float fa0 = 0.f, fb0 = 0.f, fa1 = 0.f, fb1 = 0.f;
+      if (live) {
+        fa0 = __ldg(sx_col); fb0 = __ldg(sw_row);
+        if (KT > 1) { fa1 = __ldg(sx_col + p.ld_sx); fb1 = __ldg(sw_row + 1); }
+      }
       for (int kt = 0; kt < KT; ++kt, ++it) {
-        const float s = s_next;
-        if (kt + 1 < KT && live) s_next = __ldg(sx_col + static_cast<int64_t>(kt + 1) * p.ld_sx) * __ldg(sw_row + kt + 1);
+        const float s = fa0 * fb0;
+        fa0 = fa1; fb0 = fb1;
+        if (kt + 2 < KT && live) {
+          fa1 = __ldg(sx_col + static_cast<int64_t>(kt + 2) * p.ld_sx);
+          fb1 = __ldg(sw_row + kt + 2);
+        }
+        if (p.debug == 3 || p.debug == 6) continue;   // free-running MMA: no handoff at all
         const int b = it % C::kNumAcc;
         const uint32_t aph = (it / C::kNumAcc) & 1;
         if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * BN + h * C::kCols;
+        if (p.debug == 1 || p.debug >= 4) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+          continue;
+        }
 #pragma unroll
         for (int c = 0; c < C::kCols / 32; ++c) {
           uint32_t r[32];
@@ -244,6 +281,10 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+          }
+          if (p.debug == 2) {
+            if (__uint_as_float(r[3]) == 123.456f) acc[0] += 1.0f;
+            continue;
           }
 #pragma unroll
           for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), s, acc[c * 32 + i]);
@@ -456,13 +497,19 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const bool has_col = (et < TOK) && (m0 + et < p.M);
 #pragma unroll
     for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
-    float s_next = 0.0f;
-    if (nkt > 0 && et < TOK)
-      s_next = has_col ? __ldg(p.sx + static_cast<int64_t>(kt0) * p.ld_sx + m0 + et) * __ldg(sw_row + kt0) : 0.0f;
+    float fa0 = 0.f, fb0 = 0.f, fa1 = 0.f, fb1 = 0.f;   // raw factors, two K-tiles ahead, multiplied at use
+    const float* sx_col = p.sx + m0 + et;
+    if (has_col && nkt > 0) {
+      fa0 = __ldg(sx_col + static_cast<int64_t>(kt0) * p.ld_sx); fb0 = __ldg(sw_row + kt0);
+      if (nkt > 1) { fa1 = __ldg(sx_col + static_cast<int64_t>(kt0 + 1) * p.ld_sx); fb1 = __ldg(sw_row + kt0 + 1); }
+    }
     for (int i = 0; i < nkt; ++i) {
-      const float s_mine = s_next;
-      if (i + 1 < nkt && has_col)
-        s_next = __ldg(p.sx + static_cast<int64_t>(kt0 + i + 1) * p.ld_sx + m0 + et) * __ldg(sw_row + kt0 + i + 1);
+      const float s_mine = fa0 * fb0;
+      fa0 = fa1; fb0 = fb1;
+      if (i + 2 < nkt && has_col) {
+        fa1 = __ldg(sx_col + static_cast<int64_t>(kt0 + i + 2) * p.ld_sx);
+        fb1 = __ldg(sw_row + kt0 + i + 2);
+      }
       float* scb = sc + (i & 1) * TOK;
       if (et < TOK) scb[et] = s_mine;
       const int b = i % C::kNumAcc;
@@ -599,6 +646,7 @@ int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
   p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
+  p.debug = getenv("NQ_DEBUG_EPI") ? atoi(getenv("NQ_DEBUG_EPI")) : 0;
   p.status = ctx->status_dev;
   p.wait_limit_ns = wait_limit_ns();
   const int64_t tiles = ((a.M + 127) / 128) * ((a.N + BN - 1) / BN);
