@@ -122,6 +122,7 @@ int gemm_dispatch(const GemmArgs& a, int algo) {
 }  // namespace
 }  // namespace nq
 
+namespace nq { extern long long* g_prof_buffer; }
 using namespace nq;
 
 extern "C" {
@@ -220,5 +221,10 @@ int nq_set_wait_limit_ns(uint64_t ns) {
 }
 
 int64_t nq_launch_count(void) { return g_launches.load(); }
+
+#ifdef NQ_PROFILE
+// Profiling builds only: device buffer of [grid][16] cycle counters, or null to switch accounting off.
+void nq_debug_profile_buffer(long long* device_buffer) { nq::g_prof_buffer = device_buffer; }
+#endif
 
 }  // extern "C"

@@ -24,7 +24,23 @@
 #include <cstdlib>
 #include "nq_internal.cuh"
 
+// Optional cycle accounting per role (compiled in with -DNQ_PROFILE only).
+#ifdef NQ_PROFILE
+#define NQ_PROF_DECL long long pt_[4] = {0, 0, 0, 0}; long long pt0_ = clock64();
+#define NQ_PROF_ADD(i) { const long long t_ = clock64(); pt_[i] += t_ - pt0_; pt0_ = t_; }
+#define NQ_PROF_STORE(base) if (p.prof) { for (int i_ = 0; i_ < 4; ++i_) p.prof[blockIdx.x * 16 + (base) + i_] = pt_[i_]; }
+// event trace of CTA 0: p.prof[148*16 + ev*512 + (it & 511)] = clock
+#define NQ_TRACE(ev, it) if (p.prof && blockIdx.x == 0 && (it) < 512) p.prof[148 * 16 + (ev) * 512 + (it)] = clock64();
+#else
+#define NQ_TRACE(ev, it)
+#define NQ_PROF_DECL
+#define NQ_PROF_ADD(i)
+#define NQ_PROF_STORE(base)
+#endif
+
 namespace nq {
+
+long long* g_prof_buffer = nullptr;   // device buffer [grid][16], set by nq_debug_profile_buffer (profiling builds)
 
 namespace {
 
@@ -85,8 +101,8 @@ struct TokenLane {
   static constexpr int kFirstEpiWarp = 4;           // warps 0..3: producer, MMA issuer, two idle (one warpgroup)
   static constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
   static constexpr int kCols = BN / 2;              // accumulator columns per epilogue thread
-  static constexpr int kNumAcc = 2;
-  static constexpr int kTmemCols = kNumAcc * BN;    // 512 or 256
+  static constexpr int kNumAcc = 512 / BN;          // TMEM accumulator ring: 2 x 256 or 4 x 128 columns
+  static constexpr int kTmemCols = 512;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 1024;
   static constexpr int kGroupM = 16;                // M-tiles per rasterisation group
 };
@@ -99,6 +115,8 @@ struct TokenLaneParams {
   int M, N, K;
   int y_vec;                  // 1: 16-byte stores are legal for y
   int debug;                  // experiments only: 1 = epilogue skips TMEM loads, 2 = loads but no FMA
+  long long* prof;            // cycle accounting buffer (profiling builds) or null
+  uint32_t backoff_ns; int lane0_poll;
   DeviceStatus* status;
   uint64_t wait_limit_ns;
 };
@@ -140,7 +158,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns};
+  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.backoff_ns};
 
   pdl_launch_next();
   pdl_wait_prior();   // xq / sx come from the preceding quantiser launch
@@ -160,13 +178,16 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      NQ_PROF_DECL
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int m_t, n_t;
         token_lane_tile_coords<BN>(tile, num_m, num_n, m_t, n_t);
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
+          NQ_PROF_ADD(1)
           if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteProdEmpty, kt)) { ok = false; break; }
+          NQ_PROF_ADD(0)
           uint8_t* a = smem + s * C::kStageBytes;
           if (p.debug == 4 && it >= C::kStages) {          // experiments: A only (16 KB per K-tile)
             mbar_arrive_expect_tx(&bars->full[s], kLaneTileBytes);
@@ -184,6 +205,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
       }
       issued = it;
+      NQ_PROF_STORE(0)
       if (!ok) drain_after_abort(bars, C::kStages, issued);
     }
   } else if (warp == 1) {
@@ -192,15 +214,21 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(128, BN);
       uint32_t it = 0;
       bool ok = true;
+      NQ_PROF_DECL
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int b = it % C::kNumAcc;
           const uint32_t aph = (it / C::kNumAcc) & 1;
+          NQ_PROF_ADD(2)
           if (p.debug != 3 && p.debug != 6 && !mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
+          NQ_PROF_ADD(0)
+          NQ_TRACE(0, it)
           if (!mbar_wait(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
-          tc_fence_after_sync();
+          NQ_PROF_ADD(1)
+          NQ_TRACE(1, it)
+          if (!(p.lane0_poll & 8)) tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
           const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
           const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
@@ -218,8 +246,10 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             umma_f8(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
           umma_commit(&bars->empty[s]);
           umma_commit(&bars->tmem_full[b]);
+          NQ_TRACE(2, it)
         }
       }
+      NQ_PROF_STORE(4)
       if (!ok) {   // let MMAs already issued finish before TMEM is freed
         umma_commit(&bars->teardown);
         const uint64_t t0 = globaltimer_ns();
@@ -236,6 +266,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     float acc[C::kCols];
     uint32_t it = 0;
     bool ok = true;
+    NQ_PROF_DECL
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int m_t, n_t;
       token_lane_tile_coords<BN>(tile, num_m, num_n, m_t, n_t);
@@ -263,8 +294,17 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         if (p.debug == 3 || p.debug == 6) continue;   // free-running MMA: no handoff at all
         const int b = it % C::kNumAcc;
         const uint32_t aph = (it / C::kNumAcc) & 1;
+        NQ_PROF_ADD(2)
+        if (p.lane0_poll) {
+          int good = 1;
+          if (lane == 0) good = mbar_wait(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt) ? 1 : 0;
+          good = __shfl_sync(0xFFFFFFFFu, good, 0);
+          if (!good) { ok = false; break; }
+        } else
         if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt)) { ok = false; break; }
-        tc_fence_after_sync();
+        NQ_PROF_ADD(0)
+        if (warp == C::kFirstEpiWarp && lane == 0) { NQ_TRACE(3, it) }
+        if (!(p.lane0_poll & 2)) tc_fence_after_sync();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * BN + h * C::kCols;
         if (p.debug == 1 || p.debug >= 4) {
           tc_fence_before_sync();
@@ -272,15 +312,34 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
           continue;
         }
+        if constexpr (C::kCols <= 64) {
+          // Burst drain: all columns of this thread in flight at once, accumulator handed
+          // back before any FMA is issued.
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr, r0);
+          tmem_ld_32x32(taddr + 32, r1);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+          NQ_PROF_ADD(1)
+          if (p.debug == 2) { if (__uint_as_float(r0[3]) == 123.456f) acc[0] += 1.0f; continue; }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r0[i]), s, acc[i]);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(r1[i]), s, acc[32 + i]);
+        } else {
 #pragma unroll
         for (int c = 0; c < C::kCols / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(taddr + c * 32, r);
           tmem_ld_wait();
           if (c == C::kCols / 32 - 1) {   // accumulator fully read: hand it back to the MMA warp
-            tc_fence_before_sync();
+            if (!(p.lane0_poll & 4)) tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+            NQ_PROF_ADD(1)
+            if (warp == C::kFirstEpiWarp && lane == 0) { NQ_TRACE(4, it) }
           }
           if (p.debug == 2) {
             if (__uint_as_float(r[3]) == 123.456f) acc[0] += 1.0f;
@@ -289,8 +348,10 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
           for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), s, acc[c * 32 + i]);
         }
+        }
       }
       if (!ok) break;
+      NQ_PROF_ADD(2)
       // ---- write the tile: this thread owns row m, kCols consecutive columns ----
       if (m < p.M) {
         __nv_bfloat16* yrow = p.y + static_cast<int64_t>(m) * p.ldy;
@@ -318,7 +379,12 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           }
         }
       }
+      NQ_PROF_ADD(3)
     }
+#ifdef NQ_PROFILE
+    if (warp == C::kFirstEpiWarp && lane == 0) { NQ_PROF_STORE(8) }
+    if (warp == C::kFirstEpiWarp + 7 && lane == 0) { NQ_PROF_STORE(12) }
+#endif
   }
 
   // ------------------------------ teardown ------------------------------------
@@ -354,6 +420,7 @@ struct WeightLaneParams {
   const __nv_bfloat16* bias;
   __nv_bfloat16* y; int64_t ldy;
   int M, N, K;
+  uint32_t backoff_ns;
   int splits;                 // == cluster size along grid y
   int tok_box;                // token rows per TMA box of xq (what one stage receives)
   int y_vec;                  // 1: 8-byte stores are legal for y
@@ -421,7 +488,7 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns};
+  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.backoff_ns};
   pdl_launch_next();
 
   if (warp == 0) {
@@ -647,6 +714,9 @@ int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
   p.debug = getenv("NQ_DEBUG_EPI") ? atoi(getenv("NQ_DEBUG_EPI")) : 0;
+  p.backoff_ns = getenv("NQ_BACKOFF") ? atoi(getenv("NQ_BACKOFF")) : 0;
+  p.lane0_poll = getenv("NQ_LANE0") ? atoi(getenv("NQ_LANE0")) : 0;
+  p.prof = g_prof_buffer;
   p.status = ctx->status_dev;
   p.wait_limit_ns = wait_limit_ns();
   const int64_t tiles = ((a.M + 127) / 128) * ((a.N + BN - 1) / BN);
@@ -672,6 +742,7 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
   p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.splits = splits;
+  p.backoff_ns = 0;
   p.tok_box = tokens_box;
   p.y_vec = (a.ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 8 == 0);
   p.status = ctx->status_dev;
@@ -689,6 +760,7 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
 int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
   // 128-wide tiles when the 256-wide grid would leave most SMs idle.
   const int64_t tiles256 = ((a.M + 127) / 128) * ((a.N + 255) / 256);
+  if (getenv("NQ_FORCE_BN128")) return run_token_lane<128>(a, ctx);
   if (a.N <= 128 || tiles256 * 2 <= ctx->sm_count) return run_token_lane<128>(a, ctx);
   return run_token_lane<256>(a, ctx);
 }

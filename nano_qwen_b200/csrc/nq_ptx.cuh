@@ -64,11 +64,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of the same condition (never suspends the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Shared by all roles of a CTA: raised once, never cleared during the launch.
 struct AbortCtl {
   volatile int* flag;       // in shared memory
   DeviceStatus* status;     // mapped host memory (may be null)
   uint64_t limit_ns;        // wall-clock limit for one wait
+  uint32_t backoff_ns;      // sleep between polls of a barrier that is not ready yet (0 = none)
 };
 
 static __device__ __noinline__ void report_timeout(const AbortCtl& ac, int where, int aux) {
@@ -87,12 +112,17 @@ static __device__ __noinline__ void report_timeout(const AbortCtl& ac, int where
 // aborting (this wait or another one ran out of time).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtl& ac, int where, int aux) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  // The limit is checked against the SM cycle counter (cheap to read; ~2 GHz, so
+  // 2 cycles per nanosecond is a generous conversion of the wall-clock limit).
+  const long long t0 = clock64();
+  const long long limit_cycles = static_cast<long long>(ac.limit_ns) * 2;
   for (uint32_t spin = 1;; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 0u) {
+    if (ac.backoff_ns == 1) { if (mbar_test_wait(bar, parity)) return true; }
+    else if (ac.backoff_ns > 1) { if (mbar_try_wait_hint(bar, parity, ac.backoff_ns)) return true; }
+    else if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 0u) {
       if (*ac.flag) return false;
-      if (globaltimer_ns() - t0 > ac.limit_ns) {
+      if (clock64() - t0 > limit_cycles) {
         report_timeout(ac, where, aux);
         return false;
       }
