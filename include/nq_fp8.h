@@ -57,8 +57,11 @@ extern "C" {
 
 /* Algorithm selector for the GEMM (`algo` argument). */
 #define NQ_ALGO_AUTO 0
-#define NQ_ALGO_TOKEN_LANE 1  /* tokens on the 128 UMMA lanes; 128x256 tiles; prefill-sized M */
+#define NQ_ALGO_TOKEN_LANE 1  /* tokens on the 128 UMMA lanes; 128 x {128,192,256} tiles; prefill-sized M */
 #define NQ_ALGO_WEIGHT_LANE 2 /* weight rows on the lanes (swap-AB), split-K; decode-sized M */
+#define NQ_ALGO_TOKEN_LANE_128 3 /* token-lane with a fixed tile width of 128 / 192 / 256 weight rows */
+#define NQ_ALGO_TOKEN_LANE_192 4 /* (NQ_ALGO_TOKEN_LANE picks the width itself)                        */
+#define NQ_ALGO_TOKEN_LANE_256 5
 
 /* ABI version of this header (major*100 + minor). */
 int nq_version(void);

@@ -49,7 +49,7 @@ constexpr int kLaneTileBytes = 128 * kTileK;
 
 // wait-site ids reported in DeviceStatus::where
 enum : int {
-  kSiteProdEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpiTmemFull = 4, kSiteTeardown = 5,
+  kSiteProdEmpty = 1, kSiteMmaFull = 2, kSiteMmaTmemEmpty = 3, kSiteEpiTmemFull = 4, kSiteTeardown = 5, kSiteScaleEmpty = 6,
   kSiteWeightLane = 16  // added to the above for the weight-lane kernel
 };
 
@@ -95,16 +95,27 @@ __device__ __noinline__ void drain_after_abort(PipeBars* bars, int stages, uint3
 // =========================================================================== //
 template <int BN>
 struct TokenLane {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kStageBytes = kLaneTileBytes + BN * kTileK;
-  static constexpr int kEpiWarps = 8;
-  static constexpr int kFirstEpiWarp = 4;           // warps 0..3: producer, MMA issuer, two idle (one warpgroup)
+  // BN = 192 is the balanced shape: 64 accumulator columns per epilogue thread leave room
+  // for 64 staging registers, so a whole accumulator is drained in one burst and handed
+  // back to the tensor core before any FMA is issued.  BN = 256 moves fewer operand bytes
+  // per flop but needs 128 accumulator registers per thread (drain in two halves).
+  static constexpr int kCols = (BN == 256) ? 128 : 64;        // accumulator columns per epilogue thread
+  static constexpr int kEpiGroups = BN / kCols;                // column groups: 2 (BN 128/256) or 3 (BN 192)
+  static constexpr int kEpiWarps = 4 * kEpiGroups;
+  static constexpr int kFirstEpiWarp = 4;           // warps 0..3: producer, MMA issuer, scale loader, idle
   static constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
-  static constexpr int kCols = BN / 2;              // accumulator columns per epilogue thread
-  static constexpr int kNumAcc = 512 / BN;          // TMEM accumulator ring: 2 x 256 or 4 x 128 columns
+  static constexpr int kAccStride = (BN == 128) ? 128 : 256;   // TMEM columns between accumulators
+  static constexpr int kNumAcc = 512 / kAccStride;             // accumulator ring: 4 x 128 or 2 x 192/256 columns
   static constexpr int kTmemCols = 512;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 1024;
+  static constexpr int kStageBytes = kLaneTileBytes + BN * kTileK;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 192) ? 5 : 6;
+  static constexpr int kScaleBytes = kNumAcc * kEpiGroups * 128 * 4;   // scale product per accumulator, column group, row
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + 1024;
   static constexpr int kGroupM = 16;                // M-tiles per rasterisation group
+  static constexpr int kScalePrefetch = 4;          // K-tiles of scale factors in flight in the loader warp
+  // register split between the first warpgroup and the epilogue warpgroups (setmaxnreg)
+  static constexpr int kRegsLow = 56;
+  static constexpr int kRegsHigh = (kThreads == 512) ? 152 : 224;
 };
 
 struct TokenLaneParams {
@@ -114,9 +125,10 @@ struct TokenLaneParams {
   __nv_bfloat16* y; int64_t ldy;
   int M, N, K;
   int y_vec;                  // 1: 16-byte stores are legal for y
-  int debug;                  // experiments only: 1 = epilogue skips TMEM loads, 2 = loads but no FMA
+  int sx_vec;                 // 1: 16-byte loads of sx rows are legal
+  int debug;                  // experiments only (0 in normal operation)
   long long* prof;            // cycle accounting buffer (profiling builds) or null
-  uint32_t backoff_ns; int lane0_poll;
+  uint32_t wait_mode;         // 0 try_wait, 1 test_wait spin, >1 try_wait with that suspend hint (ns)
   DeviceStatus* status;
   uint64_t wait_limit_ns;
 };
@@ -133,6 +145,16 @@ __device__ __forceinline__ void token_lane_tile_coords(int tile, int num_m, int 
   n_t = r / gsize;
 }
 
+__device__ __forceinline__ void promote32(float* acc, const uint32_t (&r)[32], float s) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r[i]), s, acc[i]);
+}
+
+// Position of the scale loader in the (tile, K-tile) iteration space of one CTA.
+struct ScaleCursor {
+  int tile, kt, m0, n0;
+};
+
 template <int BN>
 __global__ void __launch_bounds__(TokenLane<BN>::kThreads, 1)
 token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
@@ -140,13 +162,17 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   using C = TokenLane<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align_1024(smem_raw);
-  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kStages * C::kStageBytes);
+  float* scale_ring = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);   // [kNumAcc][2][128]
+  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
-    for (int b = 0; b < C::kNumAcc; ++b) { mbar_init(&bars->tmem_full[b], 1); mbar_init(&bars->tmem_empty[b], C::kEpiWarps); }
+    for (int b = 0; b < C::kNumAcc; ++b) {
+      mbar_init(&bars->tmem_full[b], 2);            // UMMA commit + scale loader
+      mbar_init(&bars->tmem_empty[b], C::kEpiWarps);
+    }
     mbar_init(&bars->teardown, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
@@ -158,7 +184,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.backoff_ns};
+  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.wait_mode};
 
   pdl_launch_next();
   pdl_wait_prior();   // xq / sx come from the preceding quantiser launch
@@ -167,12 +193,11 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int KT = (p.K + kTileK - 1) / kTileK;
-  uint32_t issued = 0;
 
   // The epilogue holds BN/2 fp32 accumulators per thread: move registers from
-  // the producer/MMA warpgroup to the two epilogue warpgroups.
+  // the first warpgroup to the two epilogue warpgroups.
   if (warp < C::kFirstEpiWarp) {
-   setmaxnreg_dec<64>();
+   setmaxnreg_dec<C::kRegsLow>();
    if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -189,26 +214,15 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteProdEmpty, kt)) { ok = false; break; }
           NQ_PROF_ADD(0)
           uint8_t* a = smem + s * C::kStageBytes;
-          if (p.debug == 4 && it >= C::kStages) {          // experiments: A only (16 KB per K-tile)
-            mbar_arrive_expect_tx(&bars->full[s], kLaneTileBytes);
-            tma_load_2d(a, &tm_x, &bars->full[s], kt * kTileK, m_t * 128);
-            continue;
-          }
-          if (p.debug == 5 && it >= C::kStages) {          // experiments: B only (32 KB per K-tile)
-            mbar_arrive_expect_tx(&bars->full[s], BN * kTileK);
-            tma_load_2d(a + kLaneTileBytes, &tm_w, &bars->full[s], kt * kTileK, n_t * BN);
-            continue;
-          }
           mbar_arrive_expect_tx(&bars->full[s], C::kStageBytes);
           tma_load_2d(a, &tm_x, &bars->full[s], kt * kTileK, m_t * 128);
           tma_load_2d(a + kLaneTileBytes, &tm_w, &bars->full[s], kt * kTileK, n_t * BN);
         }
       }
-      issued = it;
       NQ_PROF_STORE(0)
-      if (!ok) drain_after_abort(bars, C::kStages, issued);
+      if (!ok) drain_after_abort(bars, C::kStages, it);
     }
-  } else if (warp == 1) {
+   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(128, BN);
@@ -220,7 +234,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           const int b = it % C::kNumAcc;
           const uint32_t aph = (it / C::kNumAcc) & 1;
           NQ_PROF_ADD(2)
-          if (p.debug != 3 && p.debug != 6 && !mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
+          if (p.debug != 3 && !mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
           NQ_PROF_ADD(0)
@@ -228,19 +242,11 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           if (!mbar_wait(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
           NQ_PROF_ADD(1)
           NQ_TRACE(1, it)
-          if (!(p.lane0_poll & 8)) tc_fence_after_sync();
+          tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
           const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
           const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
-          const uint32_t d = tmem_base + b * BN;
-          if (p.debug == 6 && BN == 256) {
-            constexpr uint32_t idesc_half = umma_idesc_e4m3_f32(128, 128);
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-              for (int k = 0; k < kTileK / 32; ++k)
-                umma_f8(d + hh * 128, a_desc + 2 * k, b_desc + hh * 1024 + 2 * k, idesc_half, k > 0 ? 1u : 0u);
-          } else
+          const uint32_t d = tmem_base + b * C::kAccStride;
 #pragma unroll
           for (int k = 0; k < kTileK / 32; ++k)   // 32 bytes of K per UMMA: +2 in the (addr >> 4) field
             umma_f8(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
@@ -252,16 +258,88 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       NQ_PROF_STORE(4)
       if (!ok) {   // let MMAs already issued finish before TMEM is freed
         umma_commit(&bars->teardown);
-        const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(&bars->teardown, 0) && globaltimer_ns() - t0 < 20000000ull) {}
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&bars->teardown, 0) && clock64() - t0 < 40000000ll) {}
+      }
+    }
+   } else if (warp == 2) {
+    // ------------------------------ scale loader ------------------------------
+    // Keeps the per-row scale products of the next K-tiles ready in shared memory so
+    // that the epilogue threads never wait on a global load between two drains:
+    //   ring[b][h][row] = sx[kt, m0+row] * sw[block of column half h, kt]
+    // The ring slot is the accumulator slot; this warp is the second arrival on the
+    // accumulator's "full" barrier.
+    if (p.debug != 3) {
+      const int nblk = (p.N + 127) >> 7;
+      auto place = [&](ScaleCursor& c) {
+        int m_t, n_t;
+        token_lane_tile_coords<BN>(c.tile, num_m, num_n, m_t, n_t);
+        c.m0 = m_t * 128;
+        c.n0 = n_t * BN;
+      };
+      auto advance = [&](ScaleCursor& c) {
+        if (++c.kt == KT) {
+          c.kt = 0;
+          c.tile += gridDim.x;
+          if (c.tile < num_tiles) place(c);
+        }
+      };
+      auto fetch = [&](const ScaleCursor& c, float4& v, float (&w)[C::kEpiGroups]) {
+        const int m = c.m0 + 4 * lane;
+        const float* src = p.sx + static_cast<int64_t>(c.kt) * p.ld_sx + m;
+        if (p.sx_vec && m + 3 < p.M) {
+          v = __ldg(reinterpret_cast<const float4*>(src));
+        } else {
+          v.x = (m < p.M) ? __ldg(src) : 0.f;
+          v.y = (m + 1 < p.M) ? __ldg(src + 1) : 0.f;
+          v.z = (m + 2 < p.M) ? __ldg(src + 2) : 0.f;
+          v.w = (m + 3 < p.M) ? __ldg(src + 3) : 0.f;
+        }
+#pragma unroll
+        for (int g = 0; g < C::kEpiGroups; ++g) {
+          const int nb = (c.n0 + g * C::kCols) >> 7;      // a column group never straddles a 128-block
+          w[g] = (nb < nblk) ? __ldg(p.sw + static_cast<int64_t>(nb) * p.ld_sw + c.kt) : 0.f;
+        }
+      };
+      constexpr int P = C::kScalePrefetch;
+      float4 v[P];
+      float w[P][C::kEpiGroups];
+      ScaleCursor pf{static_cast<int>(blockIdx.x), 0, 0, 0}, cs = pf;
+      if (pf.tile < num_tiles) place(pf);
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int g = 0; g < C::kEpiGroups; ++g) w[j][g] = 0.f;
+        if (pf.tile < num_tiles) { fetch(pf, v[j], w[j]); advance(pf); }
+      }
+      uint32_t it = 0;
+      bool ok = true;
+      while (ok && cs.tile < num_tiles) {
+#pragma unroll
+        for (int j = 0; j < P; ++j) {
+          if (cs.tile >= num_tiles) break;
+          const int b = it % C::kNumAcc;
+          const uint32_t aph = (it / C::kNumAcc) & 1;
+          if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteScaleEmpty, cs.kt)) { ok = false; break; }
+          float4* dst = reinterpret_cast<float4*>(scale_ring + b * (C::kEpiGroups * 128)) + lane;
+#pragma unroll
+          for (int g = 0; g < C::kEpiGroups; ++g)
+            dst[32 * g] = make_float4(v[j].x * w[j][g], v[j].y * w[j][g], v[j].z * w[j][g], v[j].w * w[j][g]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->tmem_full[b]);
+          advance(cs);
+          ++it;
+          if (pf.tile < num_tiles) { fetch(pf, v[j], w[j]); advance(pf); }
+        }
       }
     }
    }
   } else {
-    setmaxnreg_inc<216>();
+    setmaxnreg_inc<C::kRegsHigh>();
     // ------------------------------ epilogue ----------------------------------
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
-    const int h = (warp - C::kFirstEpiWarp) >> 2;   // which half of the BN columns
+    const int h = (warp - C::kFirstEpiWarp) >> 2;   // which column group of the tile
     const int row = q * 32 + lane;
     float acc[C::kCols];
     uint32_t it = 0;
@@ -272,83 +350,48 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       token_lane_tile_coords<BN>(tile, num_m, num_n, m_t, n_t);
       const int m = m_t * 128 + row;
       const int n_base = n_t * BN + h * C::kCols;
-      const bool live = (m < p.M) && (n_base < p.N);
-      const float* sx_col = p.sx + m;
-      const float* sw_row = p.sw + static_cast<int64_t>(n_base >> 7) * p.ld_sw;
 #pragma unroll
       for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
-      // Scale factors are fetched two K-tiles ahead and multiplied only when used,
-      // so their L2 latency never sits between two accumulator drains.
-      float fa0 = 0.f, fb0 = 0.f, fa1 = 0.f, fb1 = 0.f;
-      if (live) {
-        fa0 = __ldg(sx_col); fb0 = __ldg(sw_row);
-        if (KT > 1) { fa1 = __ldg(sx_col + p.ld_sx); fb1 = __ldg(sw_row + 1); }
-      }
       for (int kt = 0; kt < KT; ++kt, ++it) {
-        const float s = fa0 * fb0;
-        fa0 = fa1; fb0 = fb1;
-        if (kt + 2 < KT && live) {
-          fa1 = __ldg(sx_col + static_cast<int64_t>(kt + 2) * p.ld_sx);
-          fb1 = __ldg(sw_row + kt + 2);
-        }
-        if (p.debug == 3 || p.debug == 6) continue;   // free-running MMA: no handoff at all
+        if (p.debug == 3) continue;   // experiments: free-running MMA, no handoff at all
         const int b = it % C::kNumAcc;
         const uint32_t aph = (it / C::kNumAcc) & 1;
         NQ_PROF_ADD(2)
-        if (p.lane0_poll) {
-          int good = 1;
-          if (lane == 0) good = mbar_wait(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt) ? 1 : 0;
-          good = __shfl_sync(0xFFFFFFFFu, good, 0);
-          if (!good) { ok = false; break; }
-        } else
         if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt)) { ok = false; break; }
         NQ_PROF_ADD(0)
         if (warp == C::kFirstEpiWarp && lane == 0) { NQ_TRACE(3, it) }
-        if (!(p.lane0_poll & 2)) tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * BN + h * C::kCols;
-        if (p.debug == 1 || p.debug >= 4) {
+        tc_fence_after_sync();
+        const float s = scale_ring[(b * C::kEpiGroups + h) * 128 + row];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * C::kAccStride + h * C::kCols;
+        uint32_t ra[32], rb[32];
+        if (p.debug == 1) {           // experiments: handoff only
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+          acc[0] += s;
           continue;
         }
-        if constexpr (C::kCols <= 64) {
-          // Burst drain: all columns of this thread in flight at once, accumulator handed
-          // back before any FMA is issued.
-          uint32_t r0[32], r1[32];
-          tmem_ld_32x32(taddr, r0);
-          tmem_ld_32x32(taddr + 32, r1);
-          tmem_ld_wait();
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
-          NQ_PROF_ADD(1)
-          if (p.debug == 2) { if (__uint_as_float(r0[3]) == 123.456f) acc[0] += 1.0f; continue; }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r0[i]), s, acc[i]);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(r1[i]), s, acc[32 + i]);
-        } else {
-#pragma unroll
-        for (int c = 0; c < C::kCols / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          if (c == C::kCols / 32 - 1) {   // accumulator fully read: hand it back to the MMA warp
-            if (!(p.lane0_poll & 4)) tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
-            NQ_PROF_ADD(1)
-            if (warp == C::kFirstEpiWarp && lane == 0) { NQ_TRACE(4, it) }
-          }
-          if (p.debug == 2) {
-            if (__uint_as_float(r[3]) == 123.456f) acc[0] += 1.0f;
-            continue;
-          }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), s, acc[c * 32 + i]);
+        // Two TMEM loads in flight; the accumulator is handed back as soon as the
+        // last load has landed, the remaining FMAs run while the next UMMAs execute.
+        tmem_ld_32x32(taddr, ra);
+        tmem_ld_32x32(taddr + 32, rb);
+        tmem_ld_wait_on(ra);
+        tmem_ld_wait_on(rb);
+        if constexpr (C::kCols == 128) {
+          promote32(acc, ra, s);
+          tmem_ld_32x32(taddr + 64, ra);
+          promote32(acc + 32, rb, s);
+          tmem_ld_32x32(taddr + 96, rb);
+          tmem_ld_wait_on(ra);
+          tmem_ld_wait_on(rb);
         }
-        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+        NQ_PROF_ADD(1)
+        if (warp == C::kFirstEpiWarp && lane == 0) { NQ_TRACE(4, it) }
+        promote32(acc + C::kCols - 64, ra, s);
+        promote32(acc + C::kCols - 32, rb, s);
       }
       if (!ok) break;
       NQ_PROF_ADD(2)
@@ -420,7 +463,7 @@ struct WeightLaneParams {
   const __nv_bfloat16* bias;
   __nv_bfloat16* y; int64_t ldy;
   int M, N, K;
-  uint32_t backoff_ns;
+  uint32_t wait_mode;         // 0 try_wait, 1 test_wait spin, >1 try_wait with that suspend hint (ns)
   int splits;                 // == cluster size along grid y
   int tok_box;                // token rows per TMA box of xq (what one stage receives)
   int y_vec;                  // 1: 8-byte stores are legal for y
@@ -488,7 +531,7 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.backoff_ns};
+  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.wait_mode};
   pdl_launch_next();
 
   if (warp == 0) {
@@ -592,7 +635,7 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         if (col0 + c * 16 < n_umma) {
           uint32_t r[16];
           tmem_ld_32x16(taddr + c * 16, r);
-          tmem_ld_wait();
+          tmem_ld_wait_on(r);
           const float4* s4 = reinterpret_cast<const float4*>(scb + col0 + c * 16);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -713,9 +756,9 @@ int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
   p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
+  p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
   p.debug = getenv("NQ_DEBUG_EPI") ? atoi(getenv("NQ_DEBUG_EPI")) : 0;
-  p.backoff_ns = getenv("NQ_BACKOFF") ? atoi(getenv("NQ_BACKOFF")) : 0;
-  p.lane0_poll = getenv("NQ_LANE0") ? atoi(getenv("NQ_LANE0")) : 0;
+  p.wait_mode = getenv("NQ_WAIT_MODE") ? atoi(getenv("NQ_WAIT_MODE")) : 0;
   p.prof = g_prof_buffer;
   p.status = ctx->status_dev;
   p.wait_limit_ns = wait_limit_ns();
@@ -742,7 +785,7 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
   p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.splits = splits;
-  p.backoff_ns = 0;
+  p.wait_mode = getenv("NQ_WAIT_MODE") ? atoi(getenv("NQ_WAIT_MODE")) : 0;
   p.tok_box = tokens_box;
   p.y_vec = (a.ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 8 == 0);
   p.status = ctx->status_dev;
@@ -757,11 +800,14 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
 
 }  // namespace
 
-int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
-  // 128-wide tiles when the 256-wide grid would leave most SMs idle.
-  const int64_t tiles256 = ((a.M + 127) / 128) * ((a.N + 255) / 256);
-  if (getenv("NQ_FORCE_BN128")) return run_token_lane<128>(a, ctx);
-  if (a.N <= 128 || tiles256 * 2 <= ctx->sm_count) return run_token_lane<128>(a, ctx);
+int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx, int tile_n) {
+  if (tile_n == 128) return run_token_lane<128>(a, ctx);
+  if (tile_n == 192) return run_token_lane<192>(a, ctx);
+  if (tile_n == 256) return run_token_lane<256>(a, ctx);
+  // Measured on B200 (8B-shaped layers, M = 2048..16384): 256-wide tiles are fastest (fewest operand
+  // bytes per flop); 128-wide tiles only when wider ones would leave most SMs without a tile.
+  const int64_t m_tiles = (a.M + 127) / 128;
+  if (a.N <= 128 || m_tiles * ((a.N + 255) / 256) * 2 <= ctx->sm_count) return run_token_lane<128>(a, ctx);
   return run_token_lane<256>(a, ctx);
 }
 
@@ -804,6 +850,7 @@ int setup_gemm_kernels() {
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);             \
   if (e != cudaSuccess) return check_cuda(e);
   NQ_SET_SMEM(token_lane_kernel<128>, TokenLane<128>::kSmemBytes)
+  NQ_SET_SMEM(token_lane_kernel<192>, TokenLane<192>::kSmemBytes)
   NQ_SET_SMEM(token_lane_kernel<256>, TokenLane<256>::kSmemBytes)
   NQ_SET_SMEM(weight_lane_kernel<32>, WeightLane<32>::kSmemBytes)
   NQ_SET_SMEM(weight_lane_kernel<64>, WeightLane<64>::kSmemBytes)

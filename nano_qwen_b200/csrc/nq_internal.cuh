@@ -40,7 +40,7 @@ struct GemmArgs {
   cudaStream_t stream;
   bool pdl;
 };
-int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx);
+int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx, int tile_n);   // tile_n: 0 = choose, else 128/192/256
 int launch_gemm_weight_lane(const GemmArgs& a, DeviceCtx* ctx);
 size_t weight_lane_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int weight_lane_pick_split(int64_t M, int64_t N, int64_t K, int sm_count);

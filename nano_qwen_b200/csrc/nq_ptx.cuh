@@ -93,7 +93,7 @@ struct AbortCtl {
   volatile int* flag;       // in shared memory
   DeviceStatus* status;     // mapped host memory (may be null)
   uint64_t limit_ns;        // wall-clock limit for one wait
-  uint32_t backoff_ns;      // sleep between polls of a barrier that is not ready yet (0 = none)
+  uint32_t wait_mode;       // 0 try_wait, 1 test_wait spin, >1 try_wait with that suspend-time hint (ns)
 };
 
 static __device__ __noinline__ void report_timeout(const AbortCtl& ac, int where, int aux) {
@@ -117,8 +117,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   const long long t0 = clock64();
   const long long limit_cycles = static_cast<long long>(ac.limit_ns) * 2;
   for (uint32_t spin = 1;; ++spin) {
-    if (ac.backoff_ns == 1) { if (mbar_test_wait(bar, parity)) return true; }
-    else if (ac.backoff_ns > 1) { if (mbar_try_wait_hint(bar, parity, ac.backoff_ns)) return true; }
+    if (ac.wait_mode == 1) { if (mbar_test_wait(bar, parity)) return true; }
+    else if (ac.wait_mode > 1) { if (mbar_try_wait_hint(bar, parity, ac.wait_mode)) return true; }
     else if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 255u) == 0u) {
       if (*ac.flag) return false;
@@ -260,5 +260,25 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Same wait, tied to the destination registers of a load so that the compiler cannot
+// schedule a consumer of those registers ahead of it.
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+        "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+        "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+        "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+        "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+      :
+      : "memory");
+}
 
 }  // namespace nq

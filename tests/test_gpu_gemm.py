@@ -90,10 +90,19 @@ def test_token_lane_matches_oracle(ops, m, n, k):
     check(run_gemm(ops, case, ops.ALGO_TOKEN_LANE), case)
 
 
-def test_token_lane_many_tiles_persistent_loop(ops):
+@pytest.mark.parametrize("width", ["128", "192", "256"])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 128), (130, 200, 320), (256, 1024, 1024), (300, 576, 2048), (129, 4096 + 128, 128)])
+def test_token_lane_every_tile_width(ops, width, m, n, k):
+    algo = getattr(ops, "ALGO_TOKEN_LANE_" + width)
+    case = make_case(m, n, k, seed=m + n + int(width), bias=True)
+    check(run_gemm(ops, case, algo), case)
+
+
+@pytest.mark.parametrize("width", ["128", "192", "256"])
+def test_token_lane_many_tiles_persistent_loop(ops, width):
     """More output tiles than SMs: every CTA walks several tiles and ring phases wrap many times."""
     case = make_case(2304, 4352, 384, seed=11, bias=True)       # 18 x 17 tiles of 128x256 = 306 > 148
-    check(run_gemm(ops, case, ops.ALGO_TOKEN_LANE), case)
+    check(run_gemm(ops, case, getattr(ops, "ALGO_TOKEN_LANE_" + width)), case)
 
 
 def test_known_answers_exact(ops):
