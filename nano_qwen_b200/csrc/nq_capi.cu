@@ -113,7 +113,7 @@ int gemm_dispatch(const GemmArgs& a, int algo) {
   DeviceCtx* ctx = nullptr;
   st = ensure_init(&ctx);
   if (st != NQ_OK) return st;
-  if (algo == NQ_ALGO_AUTO) algo = (a.M <= 512) ? NQ_ALGO_WEIGHT_LANE : NQ_ALGO_TOKEN_LANE;
+  if (algo == NQ_ALGO_AUTO) algo = (a.M <= 64) ? NQ_ALGO_WEIGHT_LANE : NQ_ALGO_TOKEN_LANE;   // measured crossover on B200
   if (algo == NQ_ALGO_TOKEN_LANE) return launch_gemm_token_lane(a, ctx, 0);
   if (algo == NQ_ALGO_TOKEN_LANE_128) return launch_gemm_token_lane(a, ctx, 128);
   if (algo == NQ_ALGO_TOKEN_LANE_192) return launch_gemm_token_lane(a, ctx, 192);

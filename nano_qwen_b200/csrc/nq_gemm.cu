@@ -46,6 +46,7 @@ namespace {
 
 constexpr int kTileK = 128;          // bytes == elements per K-tile row; one swizzle atom
 constexpr int kLaneTileBytes = 128 * kTileK;
+constexpr int kXchStride = 260;      // floats per row of a token-lane partial tile in shared memory (256 + pad)
 
 // wait-site ids reported in DeviceStatus::where
 enum : int {
@@ -56,8 +57,8 @@ enum : int {
 struct __align__(8) PipeBars {
   uint64_t full[8];
   uint64_t empty[8];
-  uint64_t tmem_full[4];
-  uint64_t tmem_empty[4];
+  uint64_t tmem_full[8];
+  uint64_t tmem_empty[8];
   uint64_t teardown;
   uint32_t tmem_base;
   int abort_flag;
@@ -124,6 +125,7 @@ struct TokenLaneParams {
   const __nv_bfloat16* bias;
   __nv_bfloat16* y; int64_t ldy;
   int M, N, K;
+  int splits;                 // K split over a cluster (1, splits, 1); > 1 means one tile per CTA
   int y_vec;                  // 1: 16-byte stores are legal for y
   int sx_vec;                 // 1: 16-byte loads of sx rows are legal
   int debug;                  // experiments only (0 in normal operation)
@@ -132,6 +134,25 @@ struct TokenLaneParams {
   DeviceStatus* status;
   uint64_t wait_limit_ns;
 };
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_smem_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
+}
 
 template <int BN>
 __device__ __forceinline__ void token_lane_tile_coords(int tile, int num_m, int num_n, int& m_t, int& n_t) {
@@ -192,7 +213,11 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int num_m = (p.M + 127) / 128;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
-  const int KT = (p.K + kTileK - 1) / kTileK;
+  const int KT_all = (p.K + kTileK - 1) / kTileK;
+  // K split: CTA z of a cluster owns K-tiles [kt0, kt1) of its tile; unsplit launches own all of them.
+  const int z = (p.splits > 1) ? static_cast<int>(blockIdx.y) : 0;
+  const int kt0 = static_cast<int>((static_cast<int64_t>(z) * KT_all) / p.splits);
+  const int kt1 = static_cast<int>((static_cast<int64_t>(z + 1) * KT_all) / p.splits);
 
   // The epilogue holds BN/2 fp32 accumulators per thread: move registers from
   // the first warpgroup to the two epilogue warpgroups.
@@ -207,7 +232,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int m_t, n_t;
         token_lane_tile_coords<BN>(tile, num_m, num_n, m_t, n_t);
-        for (int kt = 0; kt < KT; ++kt, ++it) {
+        for (int kt = kt0; kt < kt1; ++kt, ++it) {
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
           NQ_PROF_ADD(1)
@@ -230,7 +255,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       bool ok = true;
       NQ_PROF_DECL
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        for (int kt = 0; kt < KT; ++kt, ++it) {
+        for (int kt = kt0; kt < kt1; ++kt, ++it) {
           const int b = it % C::kNumAcc;
           const uint32_t aph = (it / C::kNumAcc) & 1;
           NQ_PROF_ADD(2)
@@ -278,8 +303,8 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         c.n0 = n_t * BN;
       };
       auto advance = [&](ScaleCursor& c) {
-        if (++c.kt == KT) {
-          c.kt = 0;
+        if (++c.kt == kt1) {
+          c.kt = kt0;
           c.tile += gridDim.x;
           if (c.tile < num_tiles) place(c);
         }
@@ -304,7 +329,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       constexpr int P = C::kScalePrefetch;
       float4 v[P];
       float w[P][C::kEpiGroups];
-      ScaleCursor pf{static_cast<int>(blockIdx.x), 0, 0, 0}, cs = pf;
+      ScaleCursor pf{static_cast<int>(blockIdx.x), kt0, 0, 0}, cs = pf;
       if (pf.tile < num_tiles) place(pf);
 #pragma unroll
       for (int j = 0; j < P; ++j) {
@@ -352,7 +377,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       const int n_base = n_t * BN + h * C::kCols;
 #pragma unroll
       for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
-      for (int kt = 0; kt < KT; ++kt, ++it) {
+      for (int kt = kt0; kt < kt1; ++kt, ++it) {
         if (p.debug == 3) continue;   // experiments: free-running MMA, no handoff at all
         const int b = it % C::kNumAcc;
         const uint32_t aph = (it / C::kNumAcc) & 1;
@@ -395,6 +420,14 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       }
       if (!ok) break;
       NQ_PROF_ADD(2)
+      if (p.splits > 1) {
+        // K-split launch: the partial tile goes to shared memory (the drained pipeline stages) for the
+        // cluster-wide sum below.  Row stride 260 floats keeps 16-byte stores of a quarter-warp apart.
+        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(smem) + row * kXchStride + h * C::kCols);
+#pragma unroll
+        for (int j = 0; j < C::kCols / 4; ++j) dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+        break;
+      }
       // ---- write the tile: this thread owns row m, kCols consecutive columns ----
       if (m < p.M) {
         __nv_bfloat16* yrow = p.y + static_cast<int64_t>(m) * p.ldy;
@@ -430,6 +463,52 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #endif
   }
 
+  if (p.splits > 1) {
+    // ---- K-split launches: sum the partial tiles of the cluster in rank order (deterministic) ----
+    __syncthreads();
+    cluster_sync_all();                                  // every split's partial tile is in its shared memory
+    if (warp >= C::kFirstEpiWarp && bars->abort_flag == 0) {
+      int m_t, n_t;
+      token_lane_tile_coords<BN>(blockIdx.x, num_m, num_n, m_t, n_t);
+      const int ew = warp - C::kFirstEpiWarp;
+      constexpr int kLanesPerRow = BN / 8;               // each lane owns 8 consecutive columns
+      const int sub = lane / kLanesPerRow;               // BN 128: two rows per warp pass; BN 192: lanes >= 24 idle
+      const int cl = lane % kLanesPerRow;
+      constexpr int kRowsPerPass = (32 / kLanesPerRow) > 0 ? (32 / kLanesPerRow) : 1;
+      for (int r = z + p.splits * (ew * kRowsPerPass + sub); r < 128; r += p.splits * C::kEpiWarps * kRowsPerPass) {
+        const int m = m_t * 128 + r;
+        if (sub >= kRowsPerPass || m >= p.M) continue;
+        const uint32_t local = smem_u32(reinterpret_cast<float*>(smem) + r * kXchStride + cl * 8);
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int c = 0; c < p.splits; ++c) {             // summed in rank order
+          const float4 a0 = ld_dsmem_f4(local, static_cast<uint32_t>(c));
+          const float4 a1 = ld_dsmem_f4(local + 16, static_cast<uint32_t>(c));
+          v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w;
+          v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
+        }
+        const int n = n_t * BN + cl * 8;
+        if (n >= p.N) continue;
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
+        }
+        __nv_bfloat16* yrow = p.y + static_cast<int64_t>(m) * p.ldy;
+        if (p.y_vec && n + 8 <= p.N) {
+          uint4 o;
+          o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+          o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+          *reinterpret_cast<uint4*>(yrow + n) = o;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (n + i < p.N) yrow[n + i] = __float2bfloat16_rn(v[i]);
+        }
+      }
+    }
+    cluster_sync_all();                                  // nobody leaves while a peer may still read its shared memory
+  }
+
   // ------------------------------ teardown ------------------------------------
   tc_fence_before_sync();
   __syncthreads();
@@ -447,14 +526,17 @@ struct WeightLane {
   static constexpr int kStages = (TOK == 32) ? 5 : (TOK == 64) ? 4 : (TOK == 128) ? 6 : 4;
   static constexpr int kStageBytes = kLaneTileBytes + TOK * kTileK;
   static constexpr int kEpiWarps = (TOK == 256) ? 8 : 4;
-  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static constexpr int kFirstEpiWarp = 4;                 // warps 0..3: producer, MMA issuer, scale loader, idle
+  static constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
   static constexpr int kCols = TOK / (kEpiWarps / 4);     // accumulator columns per epilogue thread
   static constexpr int kNumAcc = (TOK == 256) ? 2 : 4;
   static constexpr int kTmemCols = (kNumAcc * TOK) < 32 ? 32 : (kNumAcc * TOK);
   static constexpr int kExchangeBytes = 128 * TOK * 4;    // fp32 partial tile, [token][weight row]
   static constexpr int kPipeBytes = kStages * kStageBytes;
   static_assert(kExchangeBytes <= kPipeBytes, "partial tile must fit in the drained pipeline stages");
-  static constexpr int kSmemBytes = 1024 + kPipeBytes + 2 * TOK * 4 + 1024;
+  static constexpr int kScaleBytes = kNumAcc * TOK * 4;   // per accumulator: scale product per token column
+  static constexpr int kSmemBytes = 1024 + kPipeBytes + kScaleBytes + 1024;
+  static constexpr int kScalePrefetch = 4;
 };
 
 struct WeightLaneParams {
@@ -471,26 +553,17 @@ struct WeightLaneParams {
   uint64_t wait_limit_ns;
 };
 
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_smem_addr, uint32_t cta_rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(remote)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ void epi_bar_sync(int nthreads) {
-  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+// acc[0..16) += r[0..16) * sc[0..16)   (sc in shared memory, read as four broadcast float4)
+__device__ __forceinline__ void promote16_cols(float* acc, const uint32_t* r, const float* sc) {
+  const float4* s4 = reinterpret_cast<const float4*>(sc);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float4 sv = s4[j];
+    acc[4 * j + 0] = fmaf(__uint_as_float(r[4 * j + 0]), sv.x, acc[4 * j + 0]);
+    acc[4 * j + 1] = fmaf(__uint_as_float(r[4 * j + 1]), sv.y, acc[4 * j + 1]);
+    acc[4 * j + 2] = fmaf(__uint_as_float(r[4 * j + 2]), sv.z, acc[4 * j + 2]);
+    acc[4 * j + 3] = fmaf(__uint_as_float(r[4 * j + 3]), sv.w, acc[4 * j + 3]);
+  }
 }
 
 // grid = (ceil(N/128), splits, ceil(M/TOK)), cluster = (1, splits, 1).
@@ -501,8 +574,8 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   using C = WeightLane<TOK>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align_1024(smem_raw);
-  float* sc = reinterpret_cast<float*>(smem + C::kPipeBytes);             // [2][TOK] scale products
-  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kPipeBytes + 2 * TOK * 4);
+  float* sc = reinterpret_cast<float*>(smem + C::kPipeBytes);             // [kNumAcc][TOK] scale products
+  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kPipeBytes + C::kScaleBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -519,7 +592,10 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
-    for (int b = 0; b < C::kNumAcc; ++b) { mbar_init(&bars->tmem_full[b], 1); mbar_init(&bars->tmem_empty[b], C::kEpiWarps); }
+    for (int b = 0; b < C::kNumAcc; ++b) {
+      mbar_init(&bars->tmem_full[b], 2);                  // UMMA commit + scale loader
+      mbar_init(&bars->tmem_empty[b], C::kEpiWarps);
+    }
     mbar_init(&bars->teardown, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
@@ -533,6 +609,12 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   const uint32_t tmem_base = bars->tmem_base;
   const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.wait_mode};
   pdl_launch_next();
+
+  float acc[C::kCols];
+  const int q = warp & 3;
+  const int h = (warp >= C::kFirstEpiWarp) ? ((warp - C::kFirstEpiWarp) >> 2) : 0;   // column half (TOK == 256 only)
+  const int col0 = h * C::kCols;
+  bool epi_ok = true;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -587,64 +669,76 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       }
       if (!ok) {
         umma_commit(&bars->teardown);
-        const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(&bars->teardown, 0) && globaltimer_ns() - t0 < 20000000ull) {}
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&bars->teardown, 0) && clock64() - t0 < 40000000ll) {}
       }
     }
-  }
-
-  float acc[C::kCols];
-  const int q = warp & 3;
-  const int h = (warp >= 2) ? ((warp - 2) >> 2) : 0;       // column half (TOK == 256 only)
-  const int col0 = h * C::kCols;
-  bool epi_ok = true;
-  if (warp >= 2) {
-    // ------------------------------ epilogue ----------------------------------
+  } else if (warp == 2) {
+    // ------------------------------ scale loader ------------------------------
+    // sc[b][c] = sx[kt, m0+c] * sw[n_t, kt] for the K-tile that accumulator b will hold; second
+    // arrival on the accumulator's "full" barrier.  Factors are fetched kScalePrefetch K-tiles ahead.
     pdl_wait_prior();                                       // sx comes from the quantiser launch
-    constexpr int kEpiThreads = 32 * C::kEpiWarps;
-    const int et = threadIdx.x - 64;                        // 0 .. kEpiThreads-1
+    constexpr int P = C::kScalePrefetch;
+    constexpr int V = (TOK + 31) / 32;                      // token columns per lane
+    float fx[P][V], fw[P];
     const float* sw_row = p.sw + static_cast<int64_t>(n_t) * p.ld_sw;
-    const bool has_col = (et < TOK) && (m0 + et < p.M);
+    auto fetch = [&](int i, float (&x)[V], float& w) {
+      const float* src = p.sx + static_cast<int64_t>(kt0 + i) * p.ld_sx + m0;
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        const int c = lane + 32 * v;
+        x[v] = (c < m_count) ? __ldg(src + c) : 0.f;
+      }
+      w = __ldg(sw_row + kt0 + i);
+    };
+#pragma unroll
+    for (int j = 0; j < P; ++j) {
+#pragma unroll
+      for (int v = 0; v < V; ++v) fx[j][v] = 0.f;
+      fw[j] = 0.f;
+      if (j < nkt) fetch(j, fx[j], fw[j]);
+    }
+    bool ok = true;
+    for (int i0 = 0; ok && i0 < nkt; i0 += P) {
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+        const int i = i0 + j;
+        if (i >= nkt) break;
+        const int b = i % C::kNumAcc;
+        const uint32_t aph = (i / C::kNumAcc) & 1;
+        if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteWeightLane + kSiteScaleEmpty, i)) { ok = false; break; }
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+          if (lane + 32 * v < TOK) sc[b * TOK + lane + 32 * v] = fx[j][v] * fw[j];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->tmem_full[b]);
+        if (i + P < nkt) fetch(i + P, fx[j], fw[j]);
+      }
+    }
+  } else if (warp >= C::kFirstEpiWarp) {
+    // ------------------------------ epilogue ----------------------------------
 #pragma unroll
     for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
-    float fa0 = 0.f, fb0 = 0.f, fa1 = 0.f, fb1 = 0.f;   // raw factors, two K-tiles ahead, multiplied at use
-    const float* sx_col = p.sx + m0 + et;
-    if (has_col && nkt > 0) {
-      fa0 = __ldg(sx_col + static_cast<int64_t>(kt0) * p.ld_sx); fb0 = __ldg(sw_row + kt0);
-      if (nkt > 1) { fa1 = __ldg(sx_col + static_cast<int64_t>(kt0 + 1) * p.ld_sx); fb1 = __ldg(sw_row + kt0 + 1); }
-    }
     for (int i = 0; i < nkt; ++i) {
-      const float s_mine = fa0 * fb0;
-      fa0 = fa1; fb0 = fb1;
-      if (i + 2 < nkt && has_col) {
-        fa1 = __ldg(sx_col + static_cast<int64_t>(kt0 + i + 2) * p.ld_sx);
-        fb1 = __ldg(sw_row + kt0 + i + 2);
-      }
-      float* scb = sc + (i & 1) * TOK;
-      if (et < TOK) scb[et] = s_mine;
       const int b = i % C::kNumAcc;
       const uint32_t aph = (i / C::kNumAcc) & 1;
-      if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteWeightLane + kSiteEpiTmemFull, i)) { epi_ok = false; }
-      // every epilogue thread reaches this barrier, also when aborting
-      epi_bar_sync(kEpiThreads);
-      if (!epi_ok || bars->abort_flag) { epi_ok = false; break; }
+      if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteWeightLane + kSiteEpiTmemFull, i)) { epi_ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * TOK + col0;
+      const float* scb = sc + b * TOK + col0;
 #pragma unroll
-      for (int c = 0; c < C::kCols / 16; ++c) {
-        if (col0 + c * 16 < n_umma) {
-          uint32_t r[16];
-          tmem_ld_32x16(taddr + c * 16, r);
+      for (int c = 0; c < C::kCols / 32; ++c) {
+        if (col0 + c * 32 + 16 < n_umma) {                  // both 16-column halves hold tokens
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
           tmem_ld_wait_on(r);
-          const float4* s4 = reinterpret_cast<const float4*>(scb + col0 + c * 16);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float4 sv = s4[j];
-            acc[c * 16 + 4 * j + 0] = fmaf(__uint_as_float(r[4 * j + 0]), sv.x, acc[c * 16 + 4 * j + 0]);
-            acc[c * 16 + 4 * j + 1] = fmaf(__uint_as_float(r[4 * j + 1]), sv.y, acc[c * 16 + 4 * j + 1]);
-            acc[c * 16 + 4 * j + 2] = fmaf(__uint_as_float(r[4 * j + 2]), sv.z, acc[c * 16 + 4 * j + 2]);
-            acc[c * 16 + 4 * j + 3] = fmaf(__uint_as_float(r[4 * j + 3]), sv.w, acc[c * 16 + 4 * j + 3]);
-          }
+          promote16_cols(acc + c * 32, r, scb + c * 32);
+          promote16_cols(acc + c * 32 + 16, r + 16, scb + c * 32 + 16);
+        } else if (col0 + c * 32 < n_umma) {
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + c * 32, r);
+          tmem_ld_wait_on(r);
+          promote16_cols(acc + c * 32, r, scb + c * 32);
         }
       }
       tc_fence_before_sync();
@@ -657,7 +751,7 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   // accumulator), so the pipeline stages are free: reuse them for the exchange.
   __syncthreads();
   float* xch = reinterpret_cast<float*>(smem);              // [TOK][128] fp32, weight row fastest
-  if (warp >= 2) {
+  if (warp >= C::kFirstEpiWarp) {
     const int nrow = q * 32 + lane;
 #pragma unroll
     for (int c = 0; c < C::kCols; ++c)
@@ -665,20 +759,23 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   }
   cluster_sync_all();   // partial tiles of all splits are visible cluster-wide
 
-  if (warp >= 2 && bars->abort_flag == 0) {
+  if (warp >= C::kFirstEpiWarp && bars->abort_flag == 0) {
     // This CTA sums tokens z, z+splits, ... over all splits in rank order (fixed
     // order => bit-identical results run to run), adds the bias and writes y.
     const uint32_t my_rank = cluster_ctarank();
-    const int et = threadIdx.x - 64;
+    const int et = threadIdx.x - 32 * C::kFirstEpiWarp;
     const int nq4 = et & 31;                               // which 4 weight rows
     const int n = n_t * 128 + nq4 * 4;
     for (int mi = static_cast<int>(my_rank) + (et >> 5) * p.splits; mi < m_count; mi += p.splits * C::kEpiWarps) {
       float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
       const uint32_t local = smem_u32(xch + mi * 128 + nq4 * 4);
-      for (int r = 0; r < p.splits; ++r) {
-        const float4 v = ld_dsmem_f4(local, static_cast<uint32_t>(r));
-        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-      }
+      float4 part[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)                          // all remote loads in flight before the first add
+        if (r < p.splits) part[r] = ld_dsmem_f4(local, static_cast<uint32_t>(r));
+#pragma unroll
+      for (int r = 0; r < 8; ++r)                          // summed in rank order
+        if (r < p.splits) { sum.x += part[r].x; sum.y += part[r].y; sum.z += part[r].z; sum.w += part[r].w; }
       if (n < p.N) {
         float v[4] = {sum.x, sum.y, sum.z, sum.w};
         if (p.bias != nullptr) {
@@ -745,26 +842,42 @@ cudaError_t launch_ex(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_
 template <int BN>
 int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
   using C = TokenLane<BN>;
+  static_assert(128 * kXchStride * 4 <= C::kStages * C::kStageBytes, "partial tile must fit in the pipeline stages");
   CUtensorMap tm_x, tm_w;
   int st = make_tmap_u8_2d(&tm_x, a.xq, a.M, a.K, a.ld_xq, 128);
   if (st != NQ_OK) return st;
   st = make_tmap_u8_2d(&tm_w, a.wq, a.N, a.K, a.ld_wq, BN);
   if (st != NQ_OK) return st;
+  const int64_t tiles = ((a.M + 127) / 128) * ((a.N + BN - 1) / BN);
+  const int64_t KT = (a.K + 127) / 128;
+  // Few tiles: split K over a cluster of 2 or 4 CTAs (larger clusters measured slower: they cannot all be
+  // placed at once), keeping the launch within one wave and at least 4 K-tiles per CTA.
+  int splits = 1;
+  if (a.split_k > 0) {
+    splits = a.split_k > 8 ? 8 : a.split_k;
+  } else {
+    while (splits < 4 && tiles * splits * 2 <= 128) splits *= 2;
+  }
+  while (splits > 1 && KT / splits < 4) --splits;
+  if (splits > KT) splits = static_cast<int>(KT);
+  if (splits < 1) splits = 1;
   TokenLaneParams p;
   p.sx = a.sx; p.ld_sx = a.ld_sx; p.sw = a.sw; p.ld_sw = a.ld_sw;
   p.bias = static_cast<const __nv_bfloat16*>(a.bias);
   p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
+  p.splits = splits;
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
   p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
   p.debug = getenv("NQ_DEBUG_EPI") ? atoi(getenv("NQ_DEBUG_EPI")) : 0;
-  p.wait_mode = getenv("NQ_WAIT_MODE") ? atoi(getenv("NQ_WAIT_MODE")) : 0;
   p.prof = g_prof_buffer;
+  p.wait_mode = 0;
   p.status = ctx->status_dev;
   p.wait_limit_ns = wait_limit_ns();
-  const int64_t tiles = ((a.M + 127) / 128) * ((a.N + BN - 1) / BN);
-  const int grid = static_cast<int>(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-  cudaError_t e = launch_ex(token_lane_kernel<BN>, dim3(grid), dim3(C::kThreads), C::kSmemBytes, a.stream, 1, a.pdl,
+  dim3 grid;
+  if (splits > 1) grid = dim3(static_cast<unsigned>(tiles), static_cast<unsigned>(splits));
+  else grid = dim3(static_cast<unsigned>(tiles < ctx->sm_count ? tiles : ctx->sm_count));
+  cudaError_t e = launch_ex(token_lane_kernel<BN>, grid, dim3(C::kThreads), C::kSmemBytes, a.stream, splits, a.pdl,
                             tm_x, tm_w, p);
   count_launch();
   return check_cuda(e);
@@ -785,7 +898,7 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
   p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.splits = splits;
-  p.wait_mode = getenv("NQ_WAIT_MODE") ? atoi(getenv("NQ_WAIT_MODE")) : 0;
+  p.wait_mode = 0;
   p.tok_box = tokens_box;
   p.y_vec = (a.ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 8 == 0);
   p.status = ctx->status_dev;
@@ -804,23 +917,23 @@ int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx, int tile_n) {
   if (tile_n == 128) return run_token_lane<128>(a, ctx);
   if (tile_n == 192) return run_token_lane<192>(a, ctx);
   if (tile_n == 256) return run_token_lane<256>(a, ctx);
-  // Measured on B200 (8B-shaped layers, M = 2048..16384): 256-wide tiles are fastest (fewest operand
-  // bytes per flop); 128-wide tiles only when wider ones would leave most SMs without a tile.
-  const int64_t m_tiles = (a.M + 127) / 128;
-  if (a.N <= 128 || m_tiles * ((a.N + 255) / 256) * 2 <= ctx->sm_count) return run_token_lane<128>(a, ctx);
+  // Measured on B200 (8B-shaped layers): 256-wide tiles are fastest (fewest operand bytes per flop);
+  // launches with few tiles split K over a cluster instead of narrowing the tile.
+  if (a.N <= 128) return run_token_lane<128>(a, ctx);
   return run_token_lane<256>(a, ctx);
 }
 
 int weight_lane_pick_split(int64_t M, int64_t N, int64_t K, int sm_count) {
+  // Measured on B200 (8B-shaped layers): the best K split is the largest power of two (cluster size <= 8)
+  // that still lets every CTA of the launch be resident at once - two CTAs per SM for <= 64 tokens, one
+  // per SM above (the ring of 128/256-token stages fills the shared memory) - with >= 2 K-tiles per CTA.
   const int64_t KT = (K + 127) / 128;
-  const int64_t n_tiles = (N + 127) / 128;
-  const int64_t m_tiles = M <= 256 ? 1 : (M + 255) / 256;
-  // aim for about two CTAs per SM, at least two K-tiles per CTA, cluster size <= 8
+  const int64_t tiles = ((N + 127) / 128) * (M <= 256 ? 1 : (M + 255) / 256);
+  const int64_t slots = static_cast<int64_t>(sm_count) * (M <= 64 ? 2 : 1);
   int best = 1;
-  for (int s = 1; s <= 8; s *= 2) {
-    if (KT / s < 2 && s > 1) break;
+  for (int s = 2; s <= 8; s *= 2) {
+    if (KT / s < 2 || tiles * s > slots) break;
     best = s;
-    if (n_tiles * m_tiles * s >= 2 * static_cast<int64_t>(sm_count)) break;
   }
   return best;
 }

@@ -99,6 +99,21 @@ def test_token_lane_every_tile_width(ops, width, m, n, k):
 
 
 @pytest.mark.parametrize("width", ["128", "192", "256"])
+@pytest.mark.parametrize("split", [2, 3, 5, 8])
+def test_token_lane_split_k_over_a_cluster(ops, width, split):
+    """Few tiles: K is split over a cluster of CTAs and the partial tiles are summed through distributed shared memory."""
+    case = make_case(200, 520, 2048 + 128, seed=split, bias=True)      # 17 K-tiles: uneven split
+    check(run_gemm(ops, case, getattr(ops, "ALGO_TOKEN_LANE_" + width), split_k=split), case)
+
+
+def test_token_lane_auto_split_for_mid_sized_batches(ops):
+    case = make_case(256, 1024, 4096, seed=21, bias=True)
+    a = run_gemm(ops, case, ops.ALGO_TOKEN_LANE)
+    check(a, case)
+    assert torch.equal(a.view(torch.int16), run_gemm(ops, case, ops.ALGO_TOKEN_LANE).view(torch.int16))
+
+
+@pytest.mark.parametrize("width", ["128", "192", "256"])
 def test_token_lane_many_tiles_persistent_loop(ops, width):
     """More output tiles than SMs: every CTA walks several tiles and ring phases wrap many times."""
     case = make_case(2304, 4352, 384, seed=11, bias=True)       # 18 x 17 tiles of 128x256 = 306 > 148
