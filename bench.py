@@ -362,8 +362,14 @@ def run_gpu_arm(args) -> None:
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
+    # Graphs that captured NCCL collectives keep the communicator busy: drop them before tearing it down,
+    # and do not let a slow communicator teardown turn a finished benchmark into a hang.
+    del graph, g2
+    torch.cuda.synchronize()
     dist.barrier()
-    dist.destroy_process_group()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def main():

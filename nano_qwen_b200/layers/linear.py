@@ -194,7 +194,16 @@ class QKVParallelLinear(ColumnParallelLinear):
 
 
 class RowParallelLinear(LinearBase):
-    """Input features split across ranks; partial outputs summed (reference ``linear.py:131-156``)."""
+    """Input features split across ranks; partial outputs summed (reference ``linear.py:131-156``).
+
+    For prefill-sized batches the sum is pipelined against the GEMM: the token rows are processed in
+    up to ``overlap_chunks`` chunks of at least ``overlap_min_rows`` rows, and the all-reduce of chunk
+    *i* (NCCL's own stream) runs while the GEMM of chunk *i+1* executes.  The result is the same tensor
+    the reference returns; under CUDA-graph capture (decode) the call stays a single GEMM + all-reduce.
+    """
+
+    overlap_chunks = 4
+    overlap_min_rows = 2048
 
     def __init__(self, input_size: int, output_size: int, bias: bool = False):
         tp_size = dist.get_world_size()
@@ -211,7 +220,23 @@ class RowParallelLinear(LinearBase):
         self._store(param, 0, shard, 1, loaded_weight.narrow(1, src_off, src_size))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = self._linear(x, self.bias if self.tp_rank == 0 else None)
-        if self.tp_size > 1:
+        bias = self.bias if self.tp_rank == 0 else None          # added once, before the sum
+        if self.tp_size == 1:
+            return self._linear(x, bias)
+        rows = x.numel() // max(x.shape[-1], 1)
+        chunks = min(self.overlap_chunks, rows // self.overlap_min_rows)
+        if chunks < 2 or not x.is_cuda or torch.cuda.is_current_stream_capturing():
+            y = self._linear(x, bias)
             dist.all_reduce(y)
-        return y
+            return y
+        x2 = x.reshape(rows, x.shape[-1])
+        y = torch.empty((rows, self.output_size), dtype=torch.bfloat16, device=x.device)
+        step = (rows + chunks - 1) // chunks
+        pending = []
+        for lo in range(0, rows, step):
+            part = y[lo:lo + step]
+            ops.fp8_linear(x2[lo:lo + step], self.weight, self.weight_scale_inv, bias, out=part)
+            pending.append(dist.all_reduce(part, async_op=True))  # overlaps the next chunk's GEMM
+        for work in pending:
+            work.wait()
+        return y.view(*x.shape[:-1], self.output_size)

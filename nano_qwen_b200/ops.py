@@ -122,10 +122,11 @@ def fp8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Ten
 
 
 def fp8_linear(x: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, bias: torch.Tensor | None = None,
-               algo: int = ALGO_AUTO, split_k: int = 0) -> torch.Tensor:
+               algo: int = ALGO_AUTO, split_k: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
     """``F.linear`` with FP8 weights: quantise ``x`` on the fly, then the FP8 GEMM.
 
-    Accepts any leading dimensions, like ``F.linear``; returns bf16.
+    Accepts any leading dimensions, like ``F.linear``; returns bf16.  ``out``, if given, is a
+    row-contiguous bf16 ``[tokens, N]`` tensor (rows may be a slice of a larger buffer).
     """
     _require_cuda(x, wq, sw, bias)
     if x.dtype != torch.bfloat16:
@@ -142,9 +143,14 @@ def fp8_linear(x: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, bias: torch.
         raise ValueError("wq needs unit stride along K")
     if sw.dim() != 2 or (sw.shape[1] > 1 and sw.stride(1) != 1):
         sw = sw.contiguous()
-    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    else:
+        if out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N) or (N > 1 and out.stride(1) != 1):
+            raise ValueError("out must be a bf16 [tokens, N] tensor with unit stride along N")
+        y = out
     if M == 0 or N == 0:
-        return y.view(*lead, N)
+        return y if out is not None else y.view(*lead, N)
     if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_contiguous()):
         bias = bias.to(torch.bfloat16).contiguous()
     G = (K + GROUP - 1) // GROUP
@@ -153,7 +159,7 @@ def fp8_linear(x: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, bias: torch.
     st = _cabi.lib().nq_fp8_linear(
         x2.data_ptr(), x2.stride(0) if M > 1 else max(K, x2.stride(0)),
         wq.data_ptr(), wq.stride(0) if N > 1 else _round_up(K, 16), sw.data_ptr(), sw.stride(0) if sw.shape[0] > 1 else G,
-        bias.data_ptr() if bias is not None else None, y.data_ptr(), N, M, N, K,
+        bias.data_ptr() if bias is not None else None, y.data_ptr(), y.stride(0) if M > 1 else N, M, N, K,
         xq.data_ptr(), sx.data_ptr(), None, 0, algo, split_k, _stream())
     _cabi.check(st, "nq_fp8_linear")
-    return y.view(*lead, N)
+    return y if out is not None else y.view(*lead, N)

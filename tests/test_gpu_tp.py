@@ -1,0 +1,112 @@
+"""Tensor-parallel layers on 2 GPUs with NCCL against the reference's own 2-rank run (skipped on 1-GPU boxes)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import GOLDEN, ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, out_path):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from nano_qwen_b200 import ops
+        from nano_qwen_b200.layers import linear as L
+        from oracle import fp8_spec as S, synth
+        ops.init()
+        weights, acts = synth.make_stack("qwen3-0.6b", 16, seed=0)
+        shapes = synth.STACKS["qwen3-0.6b"]
+        q = {n: S.quantize_weight_block128(weights[n]) for n in synth.LAYER_ORDER}
+        torch.set_default_device("cuda")
+        torch.set_default_dtype(torch.bfloat16)
+        K, N = shapes["qkv"]
+        qkv = L.QKVParallelLinear(K, 128, N // 128 - 16, 8)
+        K, N = shapes["gate_up"]
+        gu = L.MergedColumnParallelLinear(K, [N // 2, N // 2])
+        rows = {name: L.RowParallelLinear(*shapes[name]) for name in ("o_proj", "down")}
+        torch.set_default_device("cpu")
+        torch.set_default_dtype(torch.float32)
+        res = {}
+        wq, sw = q["qkv"]
+        N = shapes["qkv"][1]
+        nq = N - 2048
+        for sid, lo, hi in (("q", 0, nq), ("k", nq, nq + 1024), ("v", nq + 1024, N)):
+            qkv.weight.weight_loader(qkv.weight, wq[lo:hi], sid)
+            qkv.weight_scale_inv.weight_loader(qkv.weight_scale_inv, sw[lo // 128:hi // 128], sid)
+        res["qkv"] = qkv(acts["qkv"].cuda())
+        wq, sw = q["gate_up"]
+        N = shapes["gate_up"][1]
+        for i in range(2):
+            gu.weight.weight_loader(gu.weight, wq[i * N // 2:(i + 1) * N // 2], i)
+            gu.weight_scale_inv.weight_loader(gu.weight_scale_inv, sw[i * N // 256:(i + 1) * N // 256], i)
+        res["gate_up"] = gu(acts["gate_up"].cuda())
+        for name, row in rows.items():
+            wq, sw = q[name]
+            row.weight.weight_loader(row.weight, wq)
+            row.weight_scale_inv.weight_loader(row.weight_scale_inv, sw)
+            ks = shapes[name][0] // world
+            x = acts[name][:, rank * ks:(rank + 1) * ks].contiguous().cuda()
+            res[name] = row(x)
+            # the same call captured in a CUDA graph (the all-reduce included), as the model runner does for decode
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                row(x)
+            torch.cuda.current_stream().wait_stream(side)
+            with torch.cuda.graph(g):
+                yg = row(x)
+            g.replay()
+            torch.cuda.synchronize()
+            res[name + "_graph"] = yg.clone()
+            del g, yg                                       # a graph holding an NCCL collective pins the communicator
+        # chunked GEMM / all-reduce pipeline of prefill-sized batches against the single-shot path
+        big = torch.randn(4096, shapes["down"][0] // world, generator=torch.Generator().manual_seed(5 + rank)).to(torch.bfloat16).cuda()
+        row = rows["down"]
+        piped = row(big)
+        row.overlap_chunks = 1
+        single = row(big)
+        torch.cuda.synchronize()
+        res["pipelined_equals_single"] = (piped == single).all().to(torch.int16).reshape(1)
+        np.savez(out_path.format(rank=rank), **{k: v.cpu().view(torch.int16).numpy() for k, v in res.items()})
+        dist.barrier()
+    except BaseException:
+        import traceback
+        traceback.print_exc()
+        sys.stderr.flush()
+        os._exit(1)
+    # leave without the communicator teardown (it can block behind captured collectives)
+    sys.stdout.flush()
+    os._exit(0)
+
+
+@pytest.mark.timeout(300)
+def test_two_gpu_layers_match_the_reference_two_rank_run(tmp_path, built_library):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from oracle import fp8_spec as S
+    out = str(tmp_path / "r{rank}.npz")
+    mp.spawn(_worker, args=(2, 29671, out), nprocs=2, join=True)
+    with np.load(os.path.join(GOLDEN, "linear_tp2.npz")) as gold:
+        got = [np.load(out.format(rank=r)) for r in range(2)]
+        for r in range(2):
+            for name in ("qkv", "gate_up", "o_proj", "down"):
+                mine = torch.from_numpy(got[r][name]).view(torch.bfloat16)
+                ref = torch.from_numpy(gold[f"y_{name}_r{r}"]).view(torch.bfloat16)
+                assert S.max_rel_err(mine, ref) <= 2e-2, (name, r)
+            for name in ("o_proj", "down"):
+                assert np.array_equal(got[r][name], got[r][name + "_graph"]), name     # graph replay == eager
+            assert int(got[r]["pipelined_equals_single"][0]) == 1
+        for name in ("o_proj", "down"):
+            assert np.array_equal(got[0][name], got[1][name])                          # both ranks hold the sum
