@@ -126,6 +126,11 @@ int nq_device_status(int* code, int* where, int* block, int* aux, int reset);
 /* Wall-clock limit (nanoseconds) of one device-side wait; default 2e9. */
 int nq_set_wait_limit_ns(uint64_t ns);
 
+/* Number of SMs the persistent GEMM (token-lane, unsplit) leaves without a CTA, so that a kernel running
+ * next to it on another stream (a collective) can be scheduled at once.  Process-wide, default 0;
+ * read at launch time.  Returns the previous value, or a negative status for n < 0. */
+int nq_set_sm_reserve(int n);
+
 /* Number of kernels this library has launched on the calling process so far. */
 int64_t nq_launch_count(void);
 

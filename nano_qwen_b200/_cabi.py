@@ -32,6 +32,7 @@ SIGNATURES = {
                               c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
     "nq_device_status": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]),
     "nq_set_wait_limit_ns": (c_int, [c_uint64]),
+    "nq_set_sm_reserve": (c_int, [c_int]),
     "nq_launch_count": (c_int64, []),
 }
 

@@ -14,6 +14,7 @@ DeviceCtx g_ctx[kMaxDevices];
 std::mutex g_mu;
 std::atomic<int64_t> g_launches{0};
 std::atomic<uint64_t> g_wait_limit_ns{2000000000ull};
+std::atomic<int> g_sm_reserve{0};
 thread_local char t_cuda_err[256] = "";
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -30,6 +31,7 @@ int check_cuda(cudaError_t e) {
 }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 uint64_t wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
+int sm_reserve() { return g_sm_reserve.load(std::memory_order_relaxed); }
 
 int ensure_init(DeviceCtx** out) {
   int dev = 0;
@@ -221,6 +223,11 @@ int nq_set_wait_limit_ns(uint64_t ns) {
   if (ns == 0) return NQ_ERR_BAD_ARGUMENT;
   g_wait_limit_ns.store(ns);
   return NQ_OK;
+}
+
+int nq_set_sm_reserve(int n) {
+  if (n < 0) return NQ_ERR_BAD_ARGUMENT;
+  return g_sm_reserve.exchange(n);
 }
 
 int64_t nq_launch_count(void) { return g_launches.load(); }

@@ -876,7 +876,11 @@ int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
   p.wait_limit_ns = wait_limit_ns();
   dim3 grid;
   if (splits > 1) grid = dim3(static_cast<unsigned>(tiles), static_cast<unsigned>(splits));
-  else grid = dim3(static_cast<unsigned>(tiles < ctx->sm_count ? tiles : ctx->sm_count));
+  else {
+    int ctas = ctx->sm_count - sm_reserve();
+    if (ctas < ctx->sm_count / 2) ctas = ctx->sm_count / 2;
+    grid = dim3(static_cast<unsigned>(tiles < ctas ? tiles : ctas));
+  }
   cudaError_t e = launch_ex(token_lane_kernel<BN>, grid, dim3(C::kThreads), C::kSmemBytes, a.stream, splits, a.pdl,
                             tm_x, tm_w, p);
   count_launch();

@@ -17,6 +17,7 @@ int ensure_init(DeviceCtx** out);             // NQ_* status; *out valid on NQ_O
 int check_cuda(cudaError_t e);                // records the message, returns NQ_OK / NQ_ERR_CUDA
 void count_launch();
 uint64_t wait_limit_ns();
+int sm_reserve();
 
 // 2-D row-major uint8 tensor [rows, cols] with row stride `ld` bytes, tiled
 // into boxes of [box_rows, 128] bytes, 128-byte swizzle, zero fill out of range.

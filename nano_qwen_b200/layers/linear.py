@@ -196,14 +196,17 @@ class QKVParallelLinear(ColumnParallelLinear):
 class RowParallelLinear(LinearBase):
     """Input features split across ranks; partial outputs summed (reference ``linear.py:131-156``).
 
-    For prefill-sized batches the sum is pipelined against the GEMM: the token rows are processed in
-    up to ``overlap_chunks`` chunks of at least ``overlap_min_rows`` rows, and the all-reduce of chunk
-    *i* (NCCL's own stream) runs while the GEMM of chunk *i+1* executes.  The result is the same tensor
-    the reference returns; under CUDA-graph capture (decode) the call stays a single GEMM + all-reduce.
+    Optionally (``overlap_chunks > 1``) the sum is pipelined against the GEMM for prefill-sized batches:
+    the token rows are processed in up to ``overlap_chunks`` chunks of at least ``overlap_min_rows``
+    rows, and the all-reduce of chunk *i* (NCCL's own stream) runs while the GEMM of chunk *i+1*
+    executes on the SMs the GEMM leaves free.  Off by default: on 2 B200s it measured slower than one
+    GEMM followed by one all-reduce (the chunked GEMMs lose more than the overlap wins).  Under
+    CUDA-graph capture (decode) the call is always a single GEMM + all-reduce, like the reference.
     """
 
-    overlap_chunks = 4
+    overlap_chunks = 1
     overlap_min_rows = 2048
+    overlap_sm_reserve = 16      # SMs the chunk GEMMs leave to the all-reduce kernel that runs beside them
 
     def __init__(self, input_size: int, output_size: int, bias: bool = False):
         tp_size = dist.get_world_size()
@@ -233,10 +236,14 @@ class RowParallelLinear(LinearBase):
         y = torch.empty((rows, self.output_size), dtype=torch.bfloat16, device=x.device)
         step = (rows + chunks - 1) // chunks
         pending = []
-        for lo in range(0, rows, step):
-            part = y[lo:lo + step]
-            ops.fp8_linear(x2[lo:lo + step], self.weight, self.weight_scale_inv, bias, out=part)
-            pending.append(dist.all_reduce(part, async_op=True))  # overlaps the next chunk's GEMM
+        old = ops.set_sm_reserve(self.overlap_sm_reserve)
+        try:
+            for lo in range(0, rows, step):
+                part = y[lo:lo + step]
+                ops.fp8_linear(x2[lo:lo + step], self.weight, self.weight_scale_inv, bias, out=part)
+                pending.append(dist.all_reduce(part, async_op=True))  # overlaps the next chunk's GEMM
+        finally:
+            ops.set_sm_reserve(old)
         for work in pending:
             work.wait()
         return y.view(*x.shape[:-1], self.output_size)

@@ -37,6 +37,14 @@ def init() -> None:
     _cabi.check(_cabi.lib().nq_init(), "nq_init")
 
 
+def set_sm_reserve(n: int) -> int:
+    """SMs the persistent GEMM leaves free for a kernel running beside it (a collective); returns the old value."""
+    old = _cabi.lib().nq_set_sm_reserve(int(n))
+    if old < 0:
+        _cabi.check(old, "nq_set_sm_reserve")
+    return old
+
+
 def launch_count() -> int:
     return int(_cabi.lib().nq_launch_count())
 
