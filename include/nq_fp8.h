@@ -117,6 +117,29 @@ int nq_fp8_linear(const void* x, int64_t ldx,
                   void* workspace, size_t workspace_bytes,
                   int algo, int split_k, void* stream);
 
+/* Capacity of the built-in scratch of nq_fp8_linear_noalloc. */
+#define NQ_NOALLOC_MAX_XQ_BYTES (8u << 20)   /* M * (K rounded up to 16)            must not exceed this */
+#define NQ_NOALLOC_MAX_SX_FLOATS (64u << 10) /* ceil(K/128) * (M rounded up to 4)   must not exceed this */
+
+/* nq_fp8_linear without any scratch argument, for callers that cannot allocate device memory (a host that
+ * only passes pre-registered tensors, a fixed memory budget, a call made while a stream is being captured).
+ * No counterpart in the reference: nano_qwen allocates freely through torch.
+ * The quantised activations go to a fixed array inside the library image (8.25 MiB, present on every GPU
+ * that loads the library until the process exits), so:
+ *   - M * roundup(K,16) <= NQ_NOALLOC_MAX_XQ_BYTES and ceil(K/128) * roundup(M,4) <= NQ_NOALLOC_MAX_SX_FLOATS,
+ *     otherwise NQ_ERR_WORKSPACE is returned and nothing is launched;
+ *   - all calls on one GPU share that array: two calls that may run at the same time on the GPU (different
+ *     streams) corrupt each other; calls on one stream are safe;
+ *   - the first call on each device looks up the array's device address (a host-side CUDA call); make that
+ *     first call, or nq_init plus one call, before starting a stream capture.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.  Inputs, outputs and all other
+ * arguments are those of nq_fp8_linear. */
+int nq_fp8_linear_noalloc(const void* x, int64_t ldx,
+                          const void* wq, int64_t ld_wq, const float* sw, int64_t ld_sw,
+                          const void* bias, void* y, int64_t ldy,
+                          int64_t M, int64_t N, int64_t K,
+                          int algo, int split_k, void* stream);
+
 /* Reads the device-side status block of the current device (mapped host
  * memory; call after synchronising the stream).  code = 0 or
  * NQ_ERR_DEVICE_TIMEOUT, where/block/aux say which wait expired.  `reset`

@@ -30,6 +30,9 @@ SIGNATURES = {
     "nq_fp8_linear": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                               c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                               c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
+    "nq_fp8_linear_noalloc": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                      c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                      c_int, c_int, c_void_p]),
     "nq_device_status": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]),
     "nq_set_wait_limit_ns": (c_int, [c_uint64]),
     "nq_set_sm_reserve": (c_int, [c_int]),
