@@ -12,6 +12,25 @@ namespace nq {
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
 
+// x / s, correctly rounded, for many x and one s.  With y = RN(1/s): q0 = RN(x*y), r = x - s*q0 (exact in one
+// FMA), q = RN(q0 + r*y) equals RN(x/s) unless the significand of s is all ones or an exponent is extreme
+// (Markstein); those scales take the IEEE divide.  Three instructions per element instead of about ten.
+struct ExactDivider {
+  float s, y;
+  bool slow;
+  __device__ __forceinline__ explicit ExactDivider(float scale) : s(scale) {
+    const uint32_t bits = __float_as_uint(scale);
+    slow = !(scale >= 1e-30f && scale <= 1e30f) || ((bits & 0x7FFFFFu) == 0x7FFFFFu);
+    y = __frcp_rn(scale);
+  }
+  __device__ __forceinline__ float operator()(float x) const {
+    if (slow) return __fdiv_rn(x, s);
+    const float q0 = __fmul_rn(x, y);
+    const float r = __fmaf_rn(-s, q0, x);
+    return __fmaf_rn(r, y, q0);
+  }
+};
+
 __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
   const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
   const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
@@ -65,8 +84,9 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __nv_bfloat16* __r
     amax = fmaxf(amax, __shfl_xor_sync(mask8, amax, 4));
     const float scale = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
     if (l8 == 0) sx[g * ld_sx + m] = scale;
+    const ExactDivider div(scale);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __fdiv_rn(v[i], scale);
+    for (int i = 0; i < 16; ++i) v[i] = div(v[i]);
     uint4 q;
     q.x = pack4_e4m3(v[0], v[1], v[2], v[3]);
     q.y = pack4_e4m3(v[4], v[5], v[6], v[7]);

@@ -34,6 +34,21 @@ def test_act_quant_bit_exact(ops, m, k):
     assert torch.equal(bits(xq)[nz], bits(xq_ref)[nz])
 
 
+def test_act_quant_bit_exact_over_many_scales(ops):
+    """16 M elements, per-row magnitudes from 2^-60 to 2^60: the reciprocal-based exact division agrees
+    with the IEEE divide of the oracle on every byte."""
+    g = torch.Generator().manual_seed(2024)
+    x = torch.randn(4096, 4096, generator=g)
+    x = x * torch.exp2(torch.randint(-60, 61, (4096, 1), generator=g).float()) * (1 + torch.rand(4096, 1, generator=g))
+    x = x.to(torch.bfloat16)
+    xq_ref, sx_ref = S.quantize_act_group128(x)
+    xq, sx = ops.act_quant(x.cuda())
+    assert torch.equal(bits(sx), bits(sx_ref))
+    assert torch.equal(bits(xq) & 0x7F, bits(xq_ref) & 0x7F)
+    nz = (bits(xq_ref) & 0x7F) != 0
+    assert torch.equal(bits(xq)[nz], bits(xq_ref)[nz])
+
+
 def test_act_quant_edge_values(ops):
     x = torch.zeros(6, 256, dtype=torch.bfloat16)
     x[0, :128] = 1.0
