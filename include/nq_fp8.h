@@ -62,6 +62,8 @@ extern "C" {
 #define NQ_ALGO_TOKEN_LANE_128 3 /* token-lane with a fixed tile width of 128 / 192 / 256 weight rows */
 #define NQ_ALGO_TOKEN_LANE_192 4 /* (NQ_ALGO_TOKEN_LANE picks the width itself)                        */
 #define NQ_ALGO_TOKEN_LANE_256 5
+#define NQ_ALGO_TOKEN_PAIR 6 /* token-lane on CTA pairs: one 256x256 tile per two SMs (tcgen05 cta_group::2) */
+#define NQ_ALGO_TOKEN_PAIR_128 7 /* the same with 256x128 tiles (four TMEM accumulators in flight) */
 
 /* ABI version of this header (major*100 + minor). */
 int nq_version(void);

@@ -259,19 +259,19 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           const int b = it % C::kNumAcc;
           const uint32_t aph = (it / C::kNumAcc) & 1;
           NQ_PROF_ADD(2)
-          if (p.debug != 3 && !mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
+          const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
+          const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
+          const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
+          const uint32_t d = tmem_base + b * C::kAccStride;
+          if (p.debug != 3 && !mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
           NQ_PROF_ADD(0)
           NQ_TRACE(0, it)
           if (!mbar_wait(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
           NQ_PROF_ADD(1)
           NQ_TRACE(1, it)
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
-          const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
-          const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
-          const uint32_t d = tmem_base + b * C::kAccStride;
 #pragma unroll
           for (int k = 0; k < kTileK / 32; ++k)   // 32 bytes of K per UMMA: +2 in the (addr >> 4) field
             umma_f8(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
@@ -515,6 +515,308 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// =========================================================================== //
+//                        token-lane kernel, CTA pairs                          //
+// =========================================================================== //
+// Same computation as token_lane_kernel<256>, but two CTAs of a cluster share one 256 x 256 output tile:
+// each owns 128 token rows (its own A tile and TMEM accumulators) and loads only HALF of the weight
+// rows of a K-tile; one tcgen05.mma.cta_group::2 (issued by the leader CTA) multiplies 256 x 256 x 32 on
+// both SMs, reading the other half of B from the peer's shared memory.  Operand traffic per SM drops from
+// 48 KB to 32 KB per K-tile and the ring holds 6 stages.  No multicast is used: both CTAs issue plain TMA
+// loads whose completion is counted on the leader's barrier, and UMMA completion is signalled to each
+// CTA's barriers by separate commits.
+template <int BN>
+struct TokenPair {
+  static constexpr int kHalfRows = BN / 2;                      // weight rows of a K-tile that one CTA loads
+  static constexpr int kStageBytes = kLaneTileBytes + kHalfRows * kTileK;   // A: 128 tokens, B: half of the BN rows
+  static constexpr int kStages = (BN == 256) ? 6 : 8;
+  static constexpr int kEpiWarps = 8;
+  static constexpr int kFirstEpiWarp = 4;
+  static constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
+  static constexpr int kCols = BN / 2;
+  static constexpr int kNumAcc = 512 / BN;                      // 2 x 256 or 4 x 128 TMEM columns
+  static constexpr int kTmemCols = 512;
+  static constexpr int kScaleBytes = kNumAcc * 2 * 128 * 4;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + 1024;
+  static constexpr int kGroupM = 8;                             // pair-tiles (256 rows) per rasterisation group
+  static constexpr int kScalePrefetch = 4;
+};
+
+struct __align__(8) PairBars {
+  uint64_t full[8];          // used in the leader: both CTAs' loads of a stage have landed
+  uint64_t empty[8];         // per CTA: the UMMAs that read the stage are complete
+  uint64_t tmem_full[4];     // per CTA: UMMAs of the K-tile complete + local scale loader
+  uint64_t tmem_empty[4];    // used in the leader: all 16 epilogue warps of the pair have drained
+  uint64_t slot_free[4];     // per CTA: the 8 local epilogue warps have read scale slot and accumulator
+  uint64_t teardown;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int num_m2, int num_n, int& m2, int& n_t) {
+  constexpr int G = 8;
+  const int per_group = G * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * G;
+  const int gsize = min(num_m2 - first_m, G);
+  const int r = tile - group * per_group;
+  m2 = first_m + r % gsize;
+  n_t = r / gsize;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(TokenPair<BN>::kThreads, 1)
+token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                  const TokenLaneParams p) {
+  using C = TokenPair<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align_1024(smem_raw);
+  float* scale_ring = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);   // [kNumAcc][2][128]
+  PairBars* bars = reinterpret_cast<PairBars*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();              // 0 = leader (issues the UMMAs)
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int b = 0; b < C::kNumAcc; ++b) {
+      mbar_init(&bars->tmem_full[b], 2);                // pair-wide UMMA commit + local scale loader
+      mbar_init(&bars->tmem_empty[b], 2 * C::kEpiWarps);
+      mbar_init(&bars->slot_free[b], C::kEpiWarps);
+    }
+    mbar_init(&bars->teardown, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_w);
+  }
+  if (warp == 1) { tmem_alloc_pair(&bars->tmem_base, C::kTmemCols); tmem_relinquish_pair(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                                   // both CTAs' barriers and TMEM exist before anything crosses
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.wait_mode};
+
+  pdl_launch_next();
+  pdl_wait_prior();
+
+  const int num_m2 = (p.M + 255) / 256;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m2 * num_n;
+  const int KT = (p.K + kTileK - 1) / kTileK;
+
+  if (warp < C::kFirstEpiWarp) {
+   setmaxnreg_dec<56>();
+   if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        int m2, n_t;
+        pair_tile_coords(tile, num_m2, num_n, m2, n_t);
+        const int m_row = m2 * 256 + static_cast<int>(rank) * 128;
+        const int n_row = n_t * BN + static_cast<int>(rank) * C::kHalfRows;
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteProdEmpty, kt)) { ok = false; break; }
+          uint8_t* a = smem + s * C::kStageBytes;
+          const uint32_t full_leader = mapa_shared(smem_u32(&bars->full[s]), 0);
+          if (rank == 0) mbar_arrive_expect_tx(&bars->full[s], 2 * C::kStageBytes);   // both CTAs' bytes
+          tma_load_2d_pair(a, &tm_x, full_leader, kt * kTileK, m_row);
+          tma_load_2d_pair(a + kLaneTileBytes, &tm_w, full_leader, kt * kTileK, n_row);
+        }
+      }
+    }
+   } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader only) ------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_e4m3_f32(256, BN);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const int b = it % C::kNumAcc;
+          const uint32_t aph = (it / C::kNumAcc) & 1;
+          if (!mbar_wait_cluster(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          if (!mbar_wait_cluster(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
+          const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
+          const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
+          const uint32_t d = tmem_base + b * BN;
+#pragma unroll
+          for (int k = 0; k < kTileK / 32; ++k)
+            umma_f8_pair(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+          // completion goes to this stage's "empty" and this accumulator's "full" barrier of BOTH CTAs
+          umma_commit_pair(smem_u32(&bars->empty[s]));
+          umma_commit_pair(mapa_shared(smem_u32(&bars->empty[s]), 1));
+          umma_commit_pair(smem_u32(&bars->tmem_full[b]));
+          umma_commit_pair(mapa_shared(smem_u32(&bars->tmem_full[b]), 1));
+        }
+      }
+      if (!ok) {
+        umma_commit_pair(smem_u32(&bars->teardown));
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&bars->teardown, 0) && clock64() - t0 < 40000000ll) {}
+      }
+    }
+   } else if (warp == 2) {
+    // ------------------------------ scale loader (both CTAs) ------------------------------
+    const int nblk = (p.N + 127) >> 7;
+    auto place = [&](ScaleCursor& c) {
+      int m2, n_t;
+      pair_tile_coords(c.tile, num_m2, num_n, m2, n_t);
+      c.m0 = m2 * 256 + static_cast<int>(rank) * 128;
+      c.n0 = n_t * BN;
+    };
+    auto advance = [&](ScaleCursor& c) {
+      if (++c.kt == KT) {
+        c.kt = 0;
+        c.tile += num_pairs;
+        if (c.tile < num_tiles) place(c);
+      }
+    };
+    auto fetch = [&](const ScaleCursor& c, float4& v, float (&w)[2]) {
+      const int m = c.m0 + 4 * lane;
+      const float* src = p.sx + static_cast<int64_t>(c.kt) * p.ld_sx + m;
+      if (p.sx_vec && m + 3 < p.M) {
+        v = __ldg(reinterpret_cast<const float4*>(src));
+      } else {
+        v.x = (m < p.M) ? __ldg(src) : 0.f;
+        v.y = (m + 1 < p.M) ? __ldg(src + 1) : 0.f;
+        v.z = (m + 2 < p.M) ? __ldg(src + 2) : 0.f;
+        v.w = (m + 3 < p.M) ? __ldg(src + 3) : 0.f;
+      }
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const int nb = (c.n0 + g * C::kCols) >> 7;
+        w[g] = (nb < nblk) ? __ldg(p.sw + static_cast<int64_t>(nb) * p.ld_sw + c.kt) : 0.f;
+      }
+    };
+    constexpr int P = C::kScalePrefetch;
+    float4 v[P];
+    float w[P][2];
+    ScaleCursor pf{pair, 0, 0, 0}, cs = pf;
+    if (pf.tile < num_tiles) place(pf);
+#pragma unroll
+    for (int j = 0; j < P; ++j) {
+      v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      w[j][0] = 0.f; w[j][1] = 0.f;
+      if (pf.tile < num_tiles) { fetch(pf, v[j], w[j]); advance(pf); }
+    }
+    uint32_t it = 0;
+    bool ok = true;
+    while (ok && cs.tile < num_tiles) {
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+        if (cs.tile >= num_tiles) break;
+        const int b = it % C::kNumAcc;
+        const uint32_t aph = (it / C::kNumAcc) & 1;
+        if (!mbar_wait(&bars->slot_free[b], aph ^ 1, ac, kSiteScaleEmpty, cs.kt)) { ok = false; break; }
+        float4* dst = reinterpret_cast<float4*>(scale_ring + b * 256) + lane;
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+          dst[32 * g] = make_float4(v[j].x * w[j][g], v[j].y * w[j][g], v[j].z * w[j][g], v[j].w * w[j][g]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->tmem_full[b]);
+        advance(cs);
+        ++it;
+        if (pf.tile < num_tiles) { fetch(pf, v[j], w[j]); advance(pf); }
+      }
+    }
+   }
+  } else {
+    setmaxnreg_inc<224>();
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int q = warp & 3;
+    const int h = (warp - C::kFirstEpiWarp) >> 2;
+    const int row = q * 32 + lane;
+    float acc[C::kCols];
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+      int m2, n_t;
+      pair_tile_coords(tile, num_m2, num_n, m2, n_t);
+      const int m = m2 * 256 + static_cast<int>(rank) * 128 + row;
+      const int n_base = n_t * BN + h * C::kCols;
+#pragma unroll
+      for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        const int b = it % C::kNumAcc;
+        const uint32_t aph = (it / C::kNumAcc) & 1;
+        if (!mbar_wait_cluster(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt)) { ok = false; break; }
+        tc_fence_after_sync();
+        const float s = scale_ring[(b * 2 + h) * 128 + row];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * BN + h * C::kCols;
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32(taddr, ra);
+        tmem_ld_32x32(taddr + 32, rb);
+        tmem_ld_wait_on(ra);
+        tmem_ld_wait_on(rb);
+        if constexpr (C::kCols == 128) {
+          promote32(acc, ra, s);
+          tmem_ld_32x32(taddr + 64, ra);
+          promote32(acc + 32, rb, s);
+          tmem_ld_32x32(taddr + 96, rb);
+          tmem_ld_wait_on(ra);
+          tmem_ld_wait_on(rb);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->slot_free[b]);                                            // local scale loader
+          mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[b]), 0));          // the leader's UMMA issuer
+        }
+        promote32(acc + C::kCols - 64, ra, s);
+        promote32(acc + C::kCols - 32, rb, s);
+      }
+      if (!ok) break;
+      if (m < p.M) {
+        __nv_bfloat16* yrow = p.y + static_cast<int64_t>(m) * p.ldy;
+#pragma unroll
+        for (int j = 0; j < C::kCols; j += 8) {
+          const int n = n_base + j;
+          if (n >= p.N) break;
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = acc[j + i];
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
+          }
+          if (p.y_vec && n + 8 <= p.N) {
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(yrow + n) = o;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (n + i < p.N) yrow[n + i] = __float2bfloat16_rn(v[i]);
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();          // the peer's UMMAs read this CTA's shared memory; its arrivals target this CTA's barriers
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, C::kTmemCols);
   }
 }
 
@@ -887,6 +1189,50 @@ int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
   return check_cuda(e);
 }
 
+template <int BN>
+int run_token_pair(const GemmArgs& a, DeviceCtx* ctx) {
+  using C = TokenPair<BN>;
+  CUtensorMap tm_x, tm_w;
+  int st = make_tmap_u8_2d(&tm_x, a.xq, a.M, a.K, a.ld_xq, 128);
+  if (st != NQ_OK) return st;
+  st = make_tmap_u8_2d(&tm_w, a.wq, a.N, a.K, a.ld_wq, BN / 2);   // each CTA of a pair loads half of the BN rows
+  if (st != NQ_OK) return st;
+  TokenLaneParams p;
+  p.sx = a.sx; p.ld_sx = a.ld_sx; p.sw = a.sw; p.ld_sw = a.ld_sw;
+  p.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
+  p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
+  p.splits = 1;
+  p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
+  p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
+  p.debug = 0;
+  p.prof = nullptr;
+  p.wait_mode = 0;
+  p.status = ctx->status_dev;
+  p.wait_limit_ns = wait_limit_ns();
+  const int64_t tiles = ((a.M + 255) / 256) * ((a.N + BN - 1) / BN);
+  int pairs = (ctx->sm_count - sm_reserve()) / 2;
+  if (pairs < 1) pairs = 1;
+  if (tiles < pairs) pairs = static_cast<int>(tiles);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(C::kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.pdl ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, token_pair_kernel<BN>, tm_x, tm_w, p);
+  count_launch();
+  return check_cuda(e);
+}
+
 template <int TOK>
 int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
   using C = WeightLane<TOK>;
@@ -916,6 +1262,10 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
 }
 
 }  // namespace
+
+int launch_gemm_token_pair(const GemmArgs& a, DeviceCtx* ctx, int tile_n) {
+  return tile_n == 128 ? run_token_pair<128>(a, ctx) : run_token_pair<256>(a, ctx);
+}
 
 int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx, int tile_n) {
   if (tile_n == 128) return run_token_lane<128>(a, ctx);
@@ -966,6 +1316,8 @@ int setup_gemm_kernels() {
 #define NQ_SET_SMEM(kern, bytes)                                                                  \
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);             \
   if (e != cudaSuccess) return check_cuda(e);
+  NQ_SET_SMEM(token_pair_kernel<128>, TokenPair<128>::kSmemBytes)
+  NQ_SET_SMEM(token_pair_kernel<256>, TokenPair<256>::kSmemBytes)
   NQ_SET_SMEM(token_lane_kernel<128>, TokenLane<128>::kSmemBytes)
   NQ_SET_SMEM(token_lane_kernel<192>, TokenLane<192>::kSmemBytes)
   NQ_SET_SMEM(token_lane_kernel<256>, TokenLane<256>::kSmemBytes)

@@ -43,6 +43,7 @@ struct GemmArgs {
 };
 int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx, int tile_n);   // tile_n: 0 = choose, else 128/192/256
 int launch_gemm_weight_lane(const GemmArgs& a, DeviceCtx* ctx);
+int launch_gemm_token_pair(const GemmArgs& a, DeviceCtx* ctx, int tile_n);   // 256 x tile_n tiles on CTA pairs (cta_group::2)
 size_t weight_lane_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int weight_lane_pick_split(int64_t M, int64_t N, int64_t K, int sm_count);
 int setup_gemm_kernels();   // cudaFuncSetAttribute for the large dynamic shared memory

@@ -98,6 +98,15 @@ def test_token_lane_every_tile_width(ops, width, m, n, k):
     check(run_gemm(ops, case, algo), case)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (1, 128, 256), (130, 200, 320), (256, 512, 512), (300, 520, 1024),
+                                   (1000, 1024, 1024), (2304, 4352, 384), (640, 4096 + 128, 256)])
+@pytest.mark.parametrize("algo", ["ALGO_TOKEN_PAIR", "ALGO_TOKEN_PAIR_128"])
+def test_token_pair_matches_oracle(ops, m, n, k, algo):
+    """256x256 / 256x128 tiles computed by CTA pairs (one UMMA spanning two SMs)."""
+    case = make_case(m, n, k, seed=m + n + k, bias=(m % 2 == 0))
+    check(run_gemm(ops, case, getattr(ops, algo)), case)
+
+
 @pytest.mark.parametrize("width", ["128", "192", "256"])
 @pytest.mark.parametrize("split", [2, 3, 5, 8])
 def test_token_lane_split_k_over_a_cluster(ops, width, split):
@@ -122,7 +131,7 @@ def test_token_lane_many_tiles_persistent_loop(ops, width):
 
 def test_known_answers_exact(ops):
     """All-ones operands with unit scales: every output is exactly K (and K + bias)."""
-    for algo, m in ((ops.ALGO_TOKEN_LANE, 130), (ops.ALGO_WEIGHT_LANE, 20)):
+    for algo, m in ((ops.ALGO_TOKEN_LANE, 130), (ops.ALGO_WEIGHT_LANE, 20), (ops.ALGO_TOKEN_PAIR, 300)):
         n, k = 384, 1024
         one = torch.full((1,), 1.0).to(torch.float8_e4m3fn)
         xq = one.expand(m, k).contiguous()
