@@ -111,7 +111,11 @@ struct TokenLane {
   static constexpr int kStageBytes = kLaneTileBytes + BN * kTileK;
   static constexpr int kStages = (BN == 256) ? 4 : (BN == 192) ? 5 : 6;
   static constexpr int kScaleBytes = kNumAcc * kEpiGroups * 128 * 4;   // scale product per accumulator, column group, row
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + 1024;
+  // Output staging for TMA stores: per epilogue warp two buffers of 32 rows x 16 bf16 columns (BN 192 has
+  // no shared memory left for them and stores from registers).
+  static constexpr bool kTmaStore = (BN != 192);
+  static constexpr int kStoreBytes = kTmaStore ? kEpiWarps * 2048 : 0;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kStoreBytes + 1024;
   static constexpr int kGroupM = 16;                // M-tiles per rasterisation group
   static constexpr int kScalePrefetch = 4;          // K-tiles of scale factors in flight in the loader warp
   // register split between the first warpgroup and the epilogue warpgroups (setmaxnreg)
@@ -127,6 +131,7 @@ struct TokenLaneParams {
   int M, N, K;
   int splits;                 // K split over a cluster (1, splits, 1); > 1 means one tile per CTA
   int y_vec;                  // 1: 16-byte stores are legal for y
+  int y_tma;                  // 1: the output tensor map is valid (y 16-byte aligned, row stride a multiple of 16 bytes)
   int sx_vec;                 // 1: 16-byte loads of sx rows are legal
   int debug;                  // experiments only (0 in normal operation)
   long long* prof;            // cycle accounting buffer (profiling builds) or null
@@ -179,12 +184,13 @@ struct ScaleCursor {
 template <int BN>
 __global__ void __launch_bounds__(TokenLane<BN>::kThreads, 1)
 token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                  const TokenLaneParams p) {
+                  const __grid_constant__ CUtensorMap tm_y, const TokenLaneParams p) {
   using C = TokenLane<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align_1024(smem_raw);
-  float* scale_ring = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);   // [kNumAcc][2][128]
-  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes);
+  float* scale_ring = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);   // [kNumAcc][groups][128]
+  uint8_t* store_ring = smem + C::kStages * C::kStageBytes + C::kScaleBytes;            // [epilogue warp][2][32 rows x 32 B]
+  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes + C::kStoreBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -199,6 +205,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     fence_mbar_init();
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_w);
+    if (p.y_tma) tma_prefetch_desc(&tm_y);
   }
   if (warp == 1) { tmem_alloc(&bars->tmem_base, C::kTmemCols); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -429,7 +436,42 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         break;
       }
       // ---- write the tile: this thread owns row m, kCols consecutive columns ----
-      if (m < p.M) {
+      if (C::kTmaStore && p.y_tma) {
+        // Through shared memory and TMA: the warp packs 32 rows x 16 columns into one of its two staging
+        // buffers and one lane issues a bulk tensor store (rows / columns past the edge are clipped by the
+        // hardware), so the warp is back at the next tile's accumulators while the stores drain.
+        uint8_t* stg = store_ring + (warp - C::kFirstEpiWarp) * 2048;
+#pragma unroll
+        for (int j = 0; j < C::kCols; j += 16) {
+          const int n = n_base + j;
+          if (n >= p.N) break;                                  // warp-uniform
+          uint8_t* buf = stg + ((j >> 4) & 1) * 1024;
+          if (lane == 0) tma_store_wait_read<1>();              // the store that last read this buffer is done with it
+          __syncwarp();
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = acc[j + i];
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
+          }
+          uint4 o0, o1;
+          o0.x = pack_bf16x2(v[0], v[1]);   o0.y = pack_bf16x2(v[2], v[3]);
+          o0.z = pack_bf16x2(v[4], v[5]);   o0.w = pack_bf16x2(v[6], v[7]);
+          o1.x = pack_bf16x2(v[8], v[9]);   o1.y = pack_bf16x2(v[10], v[11]);
+          o1.z = pack_bf16x2(v[12], v[13]); o1.w = pack_bf16x2(v[14], v[15]);
+          uint4* dst = reinterpret_cast<uint4*>(buf + lane * 32);
+          dst[0] = o0;
+          dst[1] = o1;
+          fence_proxy_async_smem();                             // make the generic-proxy writes visible to the TMA engine
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tm_y, buf, n, m_t * 128 + q * 32);
+            tma_store_commit();
+          }
+        }
+      } else if (m < p.M) {
         __nv_bfloat16* yrow = p.y + static_cast<int64_t>(m) * p.ldy;
 #pragma unroll
         for (int j = 0; j < C::kCols; j += 8) {
@@ -457,6 +499,8 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       }
       NQ_PROF_ADD(3)
     }
+    // shared memory must stay valid until the last bulk stores have read it (and y must be complete)
+    if (C::kTmaStore && p.y_tma && lane == 0) tma_store_wait_all<0>();
 #ifdef NQ_PROFILE
     if (warp == C::kFirstEpiWarp && lane == 0) { NQ_PROF_STORE(8) }
     if (warp == C::kFirstEpiWarp + 7 && lane == 0) { NQ_PROF_STORE(12) }
@@ -1170,6 +1214,13 @@ int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.splits = splits;
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
+  p.y_tma = 0;
+  CUtensorMap tm_y = tm_x;                                     // placeholder when TMA stores are not possible
+  if (C::kTmaStore && p.y_vec && splits == 1 && !getenv("NQ_NO_TMA_STORE")) {
+    st = make_tmap_bf16_2d(&tm_y, a.y, a.M, a.N, a.ldy, 32, 16);
+    if (st != NQ_OK) return st;
+    p.y_tma = 1;
+  }
   p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
   p.debug = getenv("NQ_DEBUG_EPI") ? atoi(getenv("NQ_DEBUG_EPI")) : 0;
   p.prof = g_prof_buffer;
@@ -1184,7 +1235,7 @@ int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
     grid = dim3(static_cast<unsigned>(tiles < ctas ? tiles : ctas));
   }
   cudaError_t e = launch_ex(token_lane_kernel<BN>, grid, dim3(C::kThreads), C::kSmemBytes, a.stream, splits, a.pdl,
-                            tm_x, tm_w, p);
+                            tm_x, tm_w, tm_y, p);
   count_launch();
   return check_cuda(e);
 }
@@ -1204,6 +1255,7 @@ int run_token_pair(const GemmArgs& a, DeviceCtx* ctx) {
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.splits = 1;
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
+  p.y_tma = 0;
   p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
   p.debug = 0;
   p.prof = nullptr;

@@ -22,6 +22,8 @@ int sm_reserve();
 // 2-D row-major uint8 tensor [rows, cols] with row stride `ld` bytes, tiled
 // into boxes of [box_rows, 128] bytes, 128-byte swizzle, zero fill out of range.
 int make_tmap_u8_2d(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);
+// 2-D row-major bf16 tensor [rows, cols] with row stride `ld` elements, boxes of [box_rows, box_cols], no swizzle (stores).
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int box_cols);
 
 int launch_act_quant(const void* x, int64_t M, int64_t K, int64_t ldx, void* xq, int64_t ld_xq, float* sx,
                      int64_t ld_sx, cudaStream_t stream, bool pdl);
