@@ -60,6 +60,7 @@ struct __align__(8) PipeBars {
   uint64_t tmem_full[8];
   uint64_t tmem_empty[8];
   uint64_t teardown;
+  uint64_t teardown2;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -201,6 +202,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       mbar_init(&bars->tmem_empty[b], C::kEpiWarps);
     }
     mbar_init(&bars->teardown, 1);
+    mbar_init(&bars->teardown2, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_x);
@@ -254,15 +256,23 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       NQ_PROF_STORE(0)
       if (!ok) drain_after_abort(bars, C::kStages, it);
     }
-   } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+   } else if (warp == 1 || warp == 3) {
+    // ------------------------------ MMA issuers -------------------------------
+    // Two issuing threads, one for the even and one for the odd K-tiles of this CTA's sequence.  A thread
+    // spends several hundred cycles per K-tile on things that are not UMMA issue (two barrier waits, two
+    // commits); with a single issuer the tensor pipe sat idle for that time after every K-tile.  With two,
+    // one thread's waits overlap the other's UMMAs.  Consecutive K-tiles use different accumulators and
+    // different stages, so the two instruction streams are independent.
+    if (lane == 0 && (p.debug != 8 || warp == 1)) {
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(128, BN);
+      const uint32_t mine = (warp == 1) ? 0u : 1u;
+      const bool both = (p.debug != 8);            // experiments: debug 8 = single issuer
       uint32_t it = 0;
       bool ok = true;
       NQ_PROF_DECL
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         for (int kt = kt0; kt < kt1; ++kt, ++it) {
+          if (both && (it & 1u) != mine) continue;
           const int b = it % C::kNumAcc;
           const uint32_t aph = (it / C::kNumAcc) & 1;
           NQ_PROF_ADD(2)
@@ -287,11 +297,12 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           NQ_TRACE(2, it)
         }
       }
-      NQ_PROF_STORE(4)
+      if (warp == 1) { NQ_PROF_STORE(4) }
       if (!ok) {   // let MMAs already issued finish before TMEM is freed
-        umma_commit(&bars->teardown);
+        uint64_t* td = (warp == 1) ? &bars->teardown : &bars->teardown2;
+        umma_commit(td);
         const long long t0 = clock64();
-        while (!mbar_try_wait(&bars->teardown, 0) && clock64() - t0 < 40000000ll) {}
+        while (!mbar_try_wait(td, 0) && clock64() - t0 < 40000000ll) {}
       }
     }
    } else if (warp == 2) {
@@ -391,7 +402,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         NQ_PROF_ADD(2)
         if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt)) { ok = false; break; }
         NQ_PROF_ADD(0)
-        if (warp == C::kFirstEpiWarp && lane == 0) { NQ_TRACE(3, it) }
+        if (lane == 0) { NQ_TRACE(3 + 2 * (warp - C::kFirstEpiWarp), it) }
         tc_fence_after_sync();
         const float s = scale_ring[(b * C::kEpiGroups + h) * 128 + row];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * C::kAccStride + h * C::kCols;
@@ -421,7 +432,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
         NQ_PROF_ADD(1)
-        if (warp == C::kFirstEpiWarp && lane == 0) { NQ_TRACE(4, it) }
+        if (lane == 0) { NQ_TRACE(4 + 2 * (warp - C::kFirstEpiWarp), it) }
         promote32(acc + C::kCols - 64, ra, s);
         promote32(acc + C::kCols - 32, rb, s);
       }
