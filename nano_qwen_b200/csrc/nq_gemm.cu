@@ -906,9 +906,16 @@ struct WeightLaneParams {
   int splits;                 // == cluster size along grid y
   int tok_box;                // token rows per TMA box of xq (what one stage receives)
   int y_vec;                  // 1: 8-byte stores are legal for y
+  long long* prof;            // phase timestamps (profiling builds) or null
   DeviceStatus* status;
   uint64_t wait_limit_ns;
 };
+
+#ifdef NQ_PROFILE
+#define NQ_WL_STAMP(i) if (p.prof && threadIdx.x == (i == 1 || i == 2 ? 32 : 128)) p.prof[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = globaltimer_ns();
+#else
+#define NQ_WL_STAMP(i)
+#endif
 
 // acc[0..16) += r[0..16) * sc[0..16)   (sc in shared memory, read as four broadcast float4)
 __device__ __forceinline__ void promote16_cols(float* acc, const uint32_t* r, const float* sc) {
@@ -946,6 +953,8 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   const int kt1 = static_cast<int>((static_cast<int64_t>(z + 1) * KT) / p.splits);
   const int nkt = kt1 - kt0;
   const uint32_t stage_tx = kLaneTileBytes + p.tok_box * kTileK;
+  const int pre = min(nkt, C::kStages);                   // weight tiles requested before anything else
+  NQ_WL_STAMP(0)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
@@ -958,6 +967,14 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     fence_mbar_init();
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
+    // This thread is also the TMA producer.  Weights never depend on the preceding launch, so the first
+    // ring of weight tiles is requested right here - before the CTA-wide barrier, the TMEM allocation and
+    // the dependency wait - to shorten the time from launch to the first byte.
+    const uint64_t stream_once = l2_policy_evict_first();
+    for (int i = 0; i < pre; ++i) {
+      mbar_arrive_expect_tx(&bars->full[i], stage_tx);
+      tma_load_2d_hint(smem + i * C::kStageBytes, &tm_w, &bars->full[i], (kt0 + i) * kTileK, n_t * 128, stream_once);
+    }
   }
   if (warp == 1) { tmem_alloc(&bars->tmem_base, C::kTmemCols); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -975,16 +992,10 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    // Weights never depend on the preceding launch: their first stages are in
-    // flight before the dependency wait; activations follow after it.
+    // The first ring of weight tiles is already in flight (requested during set-up); the activation
+    // tiles of those stages follow after the dependency wait.
     if (lane == 0) {
       const uint64_t stream_once = l2_policy_evict_first();
-      const int pre = min(nkt, C::kStages);
-      for (int i = 0; i < pre; ++i) {
-        uint8_t* a = smem + i * C::kStageBytes;
-        mbar_arrive_expect_tx(&bars->full[i], stage_tx);
-        tma_load_2d_hint(a, &tm_w, &bars->full[i], (kt0 + i) * kTileK, n_t * 128, stream_once);
-      }
       pdl_wait_prior();
       for (int i = 0; i < pre; ++i)
         tma_load_2d(smem + i * C::kStageBytes + kLaneTileBytes, &tm_x, &bars->full[i], (kt0 + i) * kTileK, m0);
@@ -1013,6 +1024,8 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const int s = i % C::kStages;
         const uint32_t ph = (i / C::kStages) & 1;
         if (!mbar_wait(&bars->full[s], ph, ac, kSiteWeightLane + kSiteMmaFull, i)) { ok = false; break; }
+        if (i == 0) { NQ_WL_STAMP(1) }
+        if (i == nkt - 1) { NQ_WL_STAMP(2) }
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
         const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
@@ -1106,7 +1119,9 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
   // All MMAs of this CTA have completed (the epilogue waited for the last
   // accumulator), so the pipeline stages are free: reuse them for the exchange.
+  NQ_WL_STAMP(3)
   __syncthreads();
+  NQ_WL_STAMP(4)
   float* xch = reinterpret_cast<float*>(smem);              // [TOK][128] fp32, weight row fastest
   if (warp >= C::kFirstEpiWarp) {
     const int nrow = q * 32 + lane;
@@ -1115,6 +1130,7 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       if (col0 + c < n_umma) xch[(col0 + c) * 128 + nrow] = epi_ok ? acc[c] : 0.0f;
   }
   cluster_sync_all();   // partial tiles of all splits are visible cluster-wide
+  NQ_WL_STAMP(5)
 
   if (warp >= C::kFirstEpiWarp && bars->abort_flag == 0) {
     // This CTA sums tokens z, z+splits, ... over all splits in rank order (fixed
@@ -1123,38 +1139,63 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const int et = threadIdx.x - 32 * C::kFirstEpiWarp;
     const int nq4 = et & 31;                               // which 4 weight rows
     const int n = n_t * 128 + nq4 * 4;
-    for (int mi = static_cast<int>(my_rank) + (et >> 5) * p.splits; mi < m_count; mi += p.splits * C::kEpiWarps) {
-      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-      const uint32_t local = smem_u32(xch + mi * 128 + nq4 * 4);
-      float4 part[8];
+    auto finish_row = [&](int mi, float4 sum) {
+      if (n >= p.N) return;
+      float v[4] = {sum.x, sum.y, sum.z, sum.w};
+      if (p.bias != nullptr) {
 #pragma unroll
-      for (int r = 0; r < 8; ++r)                          // all remote loads in flight before the first add
-        if (r < p.splits) part[r] = ld_dsmem_f4(local, static_cast<uint32_t>(r));
+        for (int i = 0; i < 4; ++i)
+          if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
+      }
+      __nv_bfloat16* yp = p.y + static_cast<int64_t>(m0 + mi) * p.ldy + n;
+      if (p.y_vec && n + 4 <= p.N) {
+        uint2 o;
+        o.x = pack_bf16x2(v[0], v[1]);
+        o.y = pack_bf16x2(v[2], v[3]);
+        *reinterpret_cast<uint2*>(yp) = o;
+      } else {
 #pragma unroll
-      for (int r = 0; r < 8; ++r)                          // summed in rank order
-        if (r < p.splits) { sum.x += part[r].x; sum.y += part[r].y; sum.z += part[r].z; sum.w += part[r].w; }
-      if (n < p.N) {
-        float v[4] = {sum.x, sum.y, sum.z, sum.w};
-        if (p.bias != nullptr) {
+        for (int i = 0; i < 4; ++i)
+          if (n + i < p.N) yp[i] = __float2bfloat16_rn(v[i]);
+      }
+    };
+    const int tok_stride = p.splits * C::kEpiWarps;
+    const int mi_first = static_cast<int>(my_rank) + (et >> 5) * p.splits;
+    if (p.splits == 1) {
+      // no peers: plain reads of this CTA's own tile (the compiler pipelines them)
+#pragma unroll 4
+      for (int mi = mi_first; mi < m_count; mi += tok_stride)
+        finish_row(mi, *reinterpret_cast<const float4*>(xch + mi * 128 + nq4 * 4));
+    } else {
+      // Remote loads are slow one at a time: keep eight in flight (8 / splits token rows per pass),
+      // then add them up in rank order.
+      const int rows_per_pass = p.splits >= 8 ? 1 : 8 / p.splits;
+      for (int mi = mi_first; mi < m_count; mi += tok_stride * rows_per_pass) {
+        float4 part[8];
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
+        for (int j = 0; j < 8; ++j) {
+          const int t = j / p.splits, r = j - t * p.splits;
+          const int row = mi + t * tok_stride;
+          if (t < rows_per_pass && row < m_count)
+            part[j] = ld_dsmem_f4(smem_u32(xch + row * 128 + nq4 * 4), static_cast<uint32_t>(r));
         }
-        __nv_bfloat16* yp = p.y + static_cast<int64_t>(m0 + mi) * p.ldy + n;
-        if (p.y_vec && n + 4 <= p.N) {
-          uint2 o;
-          o.x = pack_bf16x2(v[0], v[1]);
-          o.y = pack_bf16x2(v[2], v[3]);
-          *reinterpret_cast<uint2*>(yp) = o;
-        } else {
+        for (int t = 0; t < rows_per_pass; ++t) {
+          const int row = mi + t * tok_stride;
+          if (row >= m_count) break;
+          float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            if (n + i < p.N) yp[i] = __float2bfloat16_rn(v[i]);
+          for (int j = 0; j < 8; ++j) {
+            const int tj = j / p.splits;
+            if (tj == t) { sum.x += part[j].x; sum.y += part[j].y; sum.z += part[j].z; sum.w += part[j].w; }
+          }
+          finish_row(row, sum);
         }
       }
     }
   }
+  NQ_WL_STAMP(6)
   cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
+  NQ_WL_STAMP(7)
 
   tc_fence_before_sync();
   __syncthreads();
@@ -1312,6 +1353,7 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.splits = splits;
   p.wait_mode = 0;
+  p.prof = g_prof_buffer;
   p.tok_box = tokens_box;
   p.y_vec = (a.ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 8 == 0);
   p.status = ctx->status_dev;
