@@ -172,9 +172,16 @@ __device__ __forceinline__ void token_lane_tile_coords(int tile, int num_m, int 
   n_t = r / gsize;
 }
 
+// acc[0..32) += r[0..32) * s with packed two-wide FMAs (half the issue slots of scalar FMAs).
 __device__ __forceinline__ void promote32(float* acc, const uint32_t (&r)[32], float s) {
+  const float2 s2 = make_float2(s, s);
 #pragma unroll
-  for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r[i]), s, acc[i]);
+  for (int i = 0; i < 32; i += 2) {
+    const float2 v = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), s2,
+                                make_float2(acc[i], acc[i + 1]));
+    acc[i] = v.x;
+    acc[i + 1] = v.y;
+  }
 }
 
 // Position of the scale loader in the (tile, K-tile) iteration space of one CTA.
@@ -917,16 +924,18 @@ struct WeightLaneParams {
 #define NQ_WL_STAMP(i)
 #endif
 
-// acc[0..16) += r[0..16) * sc[0..16)   (sc in shared memory, read as four broadcast float4)
+// acc[0..16) += r[0..16) * sc[0..16)   (sc in shared memory, read as four broadcast float4; packed two-wide FMAs)
 __device__ __forceinline__ void promote16_cols(float* acc, const uint32_t* r, const float* sc) {
   const float4* s4 = reinterpret_cast<const float4*>(sc);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float4 sv = s4[j];
-    acc[4 * j + 0] = fmaf(__uint_as_float(r[4 * j + 0]), sv.x, acc[4 * j + 0]);
-    acc[4 * j + 1] = fmaf(__uint_as_float(r[4 * j + 1]), sv.y, acc[4 * j + 1]);
-    acc[4 * j + 2] = fmaf(__uint_as_float(r[4 * j + 2]), sv.z, acc[4 * j + 2]);
-    acc[4 * j + 3] = fmaf(__uint_as_float(r[4 * j + 3]), sv.w, acc[4 * j + 3]);
+    const float2 lo = __ffma2_rn(make_float2(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1])),
+                                 make_float2(sv.x, sv.y), make_float2(acc[4 * j + 0], acc[4 * j + 1]));
+    const float2 hi = __ffma2_rn(make_float2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])),
+                                 make_float2(sv.z, sv.w), make_float2(acc[4 * j + 2], acc[4 * j + 3]));
+    acc[4 * j + 0] = lo.x; acc[4 * j + 1] = lo.y;
+    acc[4 * j + 2] = hi.x; acc[4 * j + 3] = hi.y;
   }
 }
 
