@@ -224,6 +224,8 @@ def run_gpu_arm(args) -> None:
     from nano_qwen_b200.layers import linear as L
     ops.init()
     tp = world
+    if args.row_overlap_chunks is not None:
+        L.RowParallelLinear.overlap_chunks = args.row_overlap_chunks
     layers = build_stack(L, ops, rank, tp)
     torch.cuda.synchronize()
 
@@ -315,6 +317,41 @@ def run_gpu_arm(args) -> None:
                 ops.fp8_gemm(dec_pre[name][0], dec_pre[name][1], layer[name].weight, layer[name].weight_scale_inv)
     ms_dec_gemm, _ = timed(g2.replay, 5, 2)
     torch.cuda.synchronize()
+
+    # ---- the other batch sizes of the contract (reported, not part of `value`): one pass over the same
+    #      36-layer stack per M; decode sizes replayed from a CUDA graph, prefill sizes eager ----
+    detail = {"decode": {}, "prefill": {}}
+    if not args.no_detail:
+        gen_d = torch.Generator(device="cuda").manual_seed(99 + rank)
+        for m, kind in [(1, "decode"), (8, "decode"), (32, "decode"), (64, "decode"), (128, "decode"), (256, "decode"),
+                        (2048, "prefill"), (8192, "prefill"), (16384, "prefill")]:
+            xs = {name: torch.randn(shape, generator=gen_d, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+                  for name, shape in input_shapes(m, tp).items()}
+            if kind == "decode":
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    run_pass(layers[:2], xs)
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                gm = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gm):
+                    run_pass(layers, xs)
+                ms, _ = timed(gm.replay, 5, 2)
+                del gm
+            else:
+                ms, _ = timed(lambda: run_pass(layers, xs), 2, 1)
+            shapes_m = {"qkv": (HIDDEN, (HEADS + 2 * KV_HEADS) * HEAD_DIM // tp), "o_proj": (HIDDEN // tp, HIDDEN),
+                        "gate_up": (HIDDEN, 2 * INTER // tp), "down": (INTER // tp, HIDDEN)}
+            bytes_layer = sum(2 * m * k + n * k + 4 * ((n + 127) // 128) * ((k + 127) // 128) + 2 * m * n
+                              for k, n in shapes_m.values())
+            layer_us = ms * 1e3 / LAYERS
+            detail[kind][str(m)] = {
+                "layer_us": round(layer_us, 2),
+                "tflops": round(FLOPS_PER_TOKEN_LAYER * m / (layer_us * 1e-6) / 1e12, 1),          # whole job
+                "hbm_gbs_per_gpu": round(bytes_layer / (layer_us * 1e-6) / 1e9, 1),
+            }
+            del xs
+        torch.cuda.synchronize()
     status = _cabi.device_status()
 
     if rank == 0:
@@ -357,6 +394,10 @@ def run_gpu_arm(args) -> None:
                        "decode_layer_us": ms_decode * 1e3 / LAYERS, "prefill_layer_us": ms_prefill * 1e3 / LAYERS,
                        "decode_hbm_gbs": decode_gbs, "decode_hbm_frac_of_measured": decode_gbs / peaks["hbm_gbs"],
                        "prefill_tflops": LAYERS * FLOPS_PER_TOKEN_LAYER * M_PREFILL / (ms_prefill * 1e-3) / 1e12},
+            "detail": {"note": "one pass of the same stack per batch size M: act quant + GEMM (+ all-reduce) per linear; "
+                               "layer_us = pass time / 36; hbm_gbs_per_gpu uses the algorithmic bytes of one rank's layer "
+                               f"(measured copy peak {peaks['hbm_gbs']} GB/s); tflops is the whole job",
+                       **detail},
             "device_status": status["code"],
         }
         if cpu is not None:
@@ -378,6 +419,9 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-detail", action="store_true", help="skip the per-batch-size sweep after the timed region")
+    ap.add_argument("--row-overlap-chunks", type=int, default=None,
+                    help="token chunks in which row-parallel layers pipeline GEMM and all-reduce (default: the layer's own)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
