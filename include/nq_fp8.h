@@ -64,6 +64,10 @@ extern "C" {
 #define NQ_ALGO_TOKEN_LANE_256 5
 #define NQ_ALGO_TOKEN_PAIR 6 /* token-lane on CTA pairs: one 256x256 tile per two SMs (tcgen05 cta_group::2) */
 #define NQ_ALGO_TOKEN_PAIR_128 7 /* the same with 256x128 tiles (four TMEM accumulators in flight) */
+#define NQ_ALGO_WEIGHT_LANE_FUSED 8 /* nq_fp8_linear only: weight-lane with the activation quantiser inside the GEMM
+                                       kernel (M <= NQ_FUSED_MAX_TOKENS, K and ldx multiples of 8, x 16-byte aligned) */
+#define NQ_FUSED_MAX_TOKENS 32  /* most tokens NQ_ALGO_WEIGHT_LANE_FUSED accepts */
+#define NQ_FUSED_AUTO_TOKENS 8  /* most tokens for which NQ_ALGO_AUTO picks it */
 
 /* ABI version of this header (major*100 + minor). */
 int nq_version(void);
@@ -110,7 +114,11 @@ int nq_fp8_gemm_bs128(const void* xq, int64_t ld_xq, const float* sx, int64_t ld
 
 /* Convenience: activation quantiser + GEMM in one call.  `xq_scratch`
  * (M*ld_xq bytes, ld_xq = K rounded up to 16) and `sx_scratch`
- * (ceil(K/128)*ld_sx floats, ld_sx = M rounded up to 4) are caller-owned. */
+ * (ceil(K/128)*ld_sx floats, ld_sx = M rounded up to 4) are caller-owned.
+ * With NQ_ALGO_AUTO and M <= NQ_FUSED_AUTO_TOKENS the quantiser runs inside the
+ * GEMM kernel (NQ_ALGO_WEIGHT_LANE_FUSED: one launch, scratch untouched and
+ * allowed to be NULL) whenever x can be read 16 bytes at a time; the result is
+ * bit-identical to the two-launch path, which NQ_ALGO_WEIGHT_LANE still selects. */
 int nq_fp8_linear(const void* x, int64_t ldx,
                   const void* wq, int64_t ld_wq, const float* sw, int64_t ld_sw,
                   const void* bias, void* y, int64_t ldy,

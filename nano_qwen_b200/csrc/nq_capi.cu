@@ -218,6 +218,31 @@ int nq_fp8_linear(const void* x, int64_t ldx, const void* wq, int64_t ld_wq, con
   if (M == 0 || N == 0) return NQ_OK;
   const int64_t ld_xq = (K + 15) / 16 * 16;
   const int64_t ld_sx = (M + 3) / 4 * 4;
+  // A handful of tokens: quantise inside the weight-lane GEMM (one launch, no xq / sx round trip) when the rows
+  // of x can be read 16 bytes at a time.  Bit-identical to the two-launch path.  Every CTA of that kernel
+  // converts the activations it needs itself, which beats the separate quantiser launch up to about 8 tokens
+  // (measured on B200 with the four layer shapes of an 8B model); on request it runs up to 32.
+  const bool fusable = M <= NQ_FUSED_MAX_TOKENS && K > 0 && K % 8 == 0 && ldx % 8 == 0 && aligned16(x);
+  if (algo == NQ_ALGO_WEIGHT_LANE_FUSED && !fusable) return NQ_ERR_UNSUPPORTED;
+  if (algo == NQ_ALGO_WEIGHT_LANE_FUSED || (algo == NQ_ALGO_AUTO && fusable && M <= NQ_FUSED_AUTO_TOKENS)) {
+    if (!x || !wq || !sw || !y || ldx < K) return NQ_ERR_BAD_ARGUMENT;
+    if (!aligned16(wq) || ld_wq % 16 || ld_wq < K || ld_sw < (K + 127) / 128 || ldy < N) return NQ_ERR_BAD_ARGUMENT;
+    if (N > (1ll << 30) || K > (1ll << 30)) return NQ_ERR_UNSUPPORTED;
+    {
+      DeviceCtx* ctx = nullptr;
+      const int st0 = ensure_init(&ctx);
+      if (st0 != NQ_OK) return st0;
+      GemmArgs a;
+      a.x = x; a.ldx = ldx; a.xq = nullptr; a.ld_xq = 0; a.sx = nullptr; a.ld_sx = 0;
+      a.wq = wq; a.ld_wq = ld_wq; a.sw = sw; a.ld_sw = ld_sw;
+      a.bias = bias; a.y = y; a.ldy = ldy; a.M = M; a.N = N; a.K = K;
+      a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+      a.split_k = split_k;
+      a.stream = static_cast<cudaStream_t>(stream);
+      a.pdl = true;
+      return launch_gemm_weight_lane(a, ctx);
+    }
+  }
   int st = nq_act_quant_e4m3_g128(x, M, K, ldx, xq_scratch, ld_xq, sx_scratch, ld_sx, stream);
   if (st != NQ_OK) return st;
   return nq_fp8_gemm_bs128(xq_scratch, ld_xq, sx_scratch, ld_sx, wq, ld_wq, sw, ld_sw, bias, y, ldy, M, N, K,

@@ -23,6 +23,7 @@
 // No TMA multicast anywhere (these kernels also run in multi-GPU jobs).
 #include <cstdlib>
 #include "nq_internal.cuh"
+#include <type_traits>
 
 // Optional cycle accounting per role (compiled in with -DNQ_PROFILE only).
 #ifdef NQ_PROFILE
@@ -885,13 +886,27 @@ token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 // =========================================================================== //
 //                            weight-lane kernel                               //
 // =========================================================================== //
-template <int TOK>
+template <int TOK, bool FUSED = false>
 struct WeightLane {
   static constexpr int kStages = (TOK == 32) ? 5 : (TOK == 64) ? 4 : (TOK == 128) ? 6 : 4;
   static constexpr int kStageBytes = kLaneTileBytes + TOK * kTileK;
   static constexpr int kEpiWarps = (TOK == 256) ? 8 : 4;
   static constexpr int kFirstEpiWarp = 4;                 // warps 0..3: producer, MMA issuer, scale loader, idle
-  static constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
+  // FUSED (small decode batches, 32-token tile): the activations are quantised inside the GEMM by a third
+  // warpgroup straight into the shared-memory operand tiles; no quantiser launch, no xq / sx round trip.  Every
+  // CTA converts the activations of its own K-range again, so the work grows with tokens x weight tiles and
+  // pays off only for a handful of tokens.  Two CTAs share an SM, so the kernel starts at 80 registers per
+  // thread and the warpgroups trade them (setmaxnreg): 40 for the producer / issuer group, 96 for the
+  // epilogue, 104 for the quantisers.
+  static constexpr int kQuantWarps = FUSED ? 4 : 0;
+  static constexpr int kFirstQuantWarp = kFirstEpiWarp + kEpiWarps;
+  static constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps + kQuantWarps);
+  static constexpr int kMinCtas = (TOK <= 64) ? 2 : 1;      // decode tiles: two CTAs per SM keep more loads in flight
+  static constexpr bool kTradeRegs = FUSED;
+  static constexpr int kRegsLow = 40;
+  static constexpr int kRegsHigh = 96;
+  static constexpr int kRegsQuant = 104;
+  static_assert(!FUSED || TOK == 32, "the fused quantiser is built for the 32-token tile only");
   static constexpr int kCols = TOK / (kEpiWarps / 4);     // accumulator columns per epilogue thread
   static constexpr int kNumAcc = (TOK == 256) ? 2 : 4;
   static constexpr int kTmemCols = (kNumAcc * TOK) < 32 ? 32 : (kNumAcc * TOK);
@@ -913,6 +928,8 @@ struct WeightLaneParams {
   int splits;                 // == cluster size along grid y
   int tok_box;                // token rows per TMA box of xq (what one stage receives)
   int y_vec;                  // 1: 8-byte stores are legal for y
+  const __nv_bfloat16* x;     // FUSED kernels: unquantised activations [M, K], row stride ldx (16-byte aligned rows)
+  int64_t ldx;
   long long* prof;            // phase timestamps (profiling builds) or null
   DeviceStatus* status;
   uint64_t wait_limit_ns;
@@ -920,8 +937,10 @@ struct WeightLaneParams {
 
 #ifdef NQ_PROFILE
 #define NQ_WL_STAMP(i) if (p.prof && threadIdx.x == (i == 1 || i == 2 ? 32 : 128)) p.prof[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = globaltimer_ns();
+#define NQ_QTRACE(ev, it) if (p.prof && blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) p.prof[4096 * 8 + (ev) * 64 + (it)] = clock64();
 #else
 #define NQ_WL_STAMP(i)
+#define NQ_QTRACE(ev, it)
 #endif
 
 // acc[0..16) += r[0..16) * sc[0..16)   (sc in shared memory, read as four broadcast float4; packed two-wide FMAs)
@@ -939,120 +958,77 @@ __device__ __forceinline__ void promote16_cols(float* acc, const uint32_t* r, co
   }
 }
 
-// grid = (ceil(N/128), splits, ceil(M/TOK)), cluster = (1, splits, 1).
-template <int TOK>
-__global__ void __launch_bounds__(WeightLane<TOK>::kThreads)
-weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                   const WeightLaneParams p) {
-  using C = WeightLane<TOK>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align_1024(smem_raw);
-  float* sc = reinterpret_cast<float*>(smem + C::kPipeBytes);             // [kNumAcc][TOK] scale products
-  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kPipeBytes + C::kScaleBytes);
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-
-  const int n_t = blockIdx.x;
-  const int z = blockIdx.y;
-  const int m0 = blockIdx.z * TOK;
-  const int m_count = min(p.M - m0, TOK);
-  const int n_umma = (m_count + 15) & ~15;                // tokens padded to the UMMA N granularity
-  const int KT = (p.K + kTileK - 1) / kTileK;
-  const int kt0 = static_cast<int>((static_cast<int64_t>(z) * KT) / p.splits);
-  const int kt1 = static_cast<int>((static_cast<int64_t>(z + 1) * KT) / p.splits);
-  const int nkt = kt1 - kt0;
-  const uint32_t stage_tx = kLaneTileBytes + p.tok_box * kTileK;
-  const int pre = min(nkt, C::kStages);                   // weight tiles requested before anything else
-  NQ_WL_STAMP(0)
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
-    for (int b = 0; b < C::kNumAcc; ++b) {
-      mbar_init(&bars->tmem_full[b], 2);                  // UMMA commit + scale loader
-      mbar_init(&bars->tmem_empty[b], C::kEpiWarps);
-    }
-    mbar_init(&bars->teardown, 1);
-    bars->abort_flag = 0;
-    fence_mbar_init();
-    tma_prefetch_desc(&tm_w);
-    tma_prefetch_desc(&tm_x);
-    // This thread is also the TMA producer.  Weights never depend on the preceding launch, so the first
-    // ring of weight tiles is requested right here - before the CTA-wide barrier, the TMEM allocation and
-    // the dependency wait - to shorten the time from launch to the first byte.
-    const uint64_t stream_once = l2_policy_evict_first();
-    for (int i = 0; i < pre; ++i) {
-      mbar_arrive_expect_tx(&bars->full[i], stage_tx);
-      tma_load_2d_hint(smem + i * C::kStageBytes, &tm_w, &bars->full[i], (kt0 + i) * kTileK, n_t * 128, stream_once);
-    }
-  }
-  if (warp == 1) { tmem_alloc(&bars->tmem_base, C::kTmemCols); tmem_relinquish(); }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_base;
-  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.wait_mode};
-  pdl_launch_next();
-
-  float acc[C::kCols];
-  const int q = warp & 3;
-  const int h = (warp >= C::kFirstEpiWarp) ? ((warp - C::kFirstEpiWarp) >> 2) : 0;   // column half (TOK == 256 only)
-  const int col0 = h * C::kCols;
-  bool epi_ok = true;
-
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    // The first ring of weight tiles is already in flight (requested during set-up); the activation
-    // tiles of those stages follow after the dependency wait.
-    if (lane == 0) {
-      const uint64_t stream_once = l2_policy_evict_first();
-      pdl_wait_prior();
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d(smem + i * C::kStageBytes + kLaneTileBytes, &tm_x, &bars->full[i], (kt0 + i) * kTileK, m0);
-      bool ok = true;
-      int i = pre;
-      for (; i < nkt; ++i) {
-        const int s = i % C::kStages;
-        const uint32_t ph = (i / C::kStages) & 1;
-        if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteWeightLane + kSiteProdEmpty, i)) { ok = false; break; }
-        uint8_t* a = smem + s * C::kStageBytes;
-        mbar_arrive_expect_tx(&bars->full[s], stage_tx);
-        tma_load_2d_hint(a, &tm_w, &bars->full[s], (kt0 + i) * kTileK, n_t * 128, stream_once);
-        tma_load_2d(a + kLaneTileBytes, &tm_x, &bars->full[s], (kt0 + i) * kTileK, m0);
-      }
-      if (!ok) drain_after_abort(bars, C::kStages, static_cast<uint32_t>(i));
-    }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_e4m3_f32(128, n_umma);
-      bool ok = true;
-      for (int i = 0; i < nkt; ++i) {
-        const int b = i % C::kNumAcc;
-        const uint32_t aph = (i / C::kNumAcc) & 1;
-        if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteWeightLane + kSiteMmaTmemEmpty, i)) { ok = false; break; }
-        const int s = i % C::kStages;
-        const uint32_t ph = (i / C::kStages) & 1;
-        if (!mbar_wait(&bars->full[s], ph, ac, kSiteWeightLane + kSiteMmaFull, i)) { ok = false; break; }
-        if (i == 0) { NQ_WL_STAMP(1) }
-        if (i == nkt - 1) { NQ_WL_STAMP(2) }
-        tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
-        const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
-        const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
-        const uint32_t d = tmem_base + b * TOK;
+// Rare path of quantise_rows_e4m3: a scale whose reciprocal trick is not exact; plain IEEE divisions.
+__device__ __noinline__ uint2 quantise8_e4m3_ieee(uint4 raw, float scale) {
+  const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+  float v[8];
 #pragma unroll
-        for (int k = 0; k < kTileK / 32; ++k)
-          umma_f8(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
-        umma_commit(&bars->empty[s]);
-        umma_commit(&bars->tmem_full[b]);
-      }
-      if (!ok) {
-        umma_commit(&bars->teardown);
-        const long long t0 = clock64();
-        while (!mbar_try_wait(&bars->teardown, 0) && clock64() - t0 < 40000000ll) {}
-      }
+  for (int e = 0; e < 4; ++e) {
+    v[2 * e] = __fdiv_rn(bf16_bits_to_float(w4[e] & 0xFFFFu), scale);
+    v[2 * e + 1] = __fdiv_rn(bf16_bits_to_float(w4[e] >> 16), scale);
+  }
+  return make_uint2(pack4_e4m3(v[0], v[1], v[2], v[3]), pack4_e4m3(v[4], v[5], v[6], v[7]));
+}
+
+// Dynamic 1x128 quantisation of NR token rows at once, 16 lanes per row (8 consecutive bf16 per lane, given as
+// raw bits), both 16-lane halves of the warp busy on different rows: per row amax -> scale = max(amax, 1e-10) /
+// 448 -> q = RNE_e4m3(x / scale), the arithmetic of act_quant_kernel.  The whole warp must call it together.
+template <int NR>
+__device__ __forceinline__ void quantise_rows_e4m3(const uint4 (&raw)[NR], uint32_t mask16, uint2 (&q)[NR],
+                                                   float (&scale)[NR]) {
+  float v[NR][8], y[NR];
+  bool slow = false;
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    const uint32_t w4[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      v[r][2 * e] = bf16_bits_to_float(w4[e] & 0xFFFFu);
+      v[r][2 * e + 1] = bf16_bits_to_float(w4[e] >> 16);
     }
-  } else if (warp == 2) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[r][e]));
+    amax = fmaxf(amax, __shfl_xor_sync(mask16, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(mask16, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(mask16, amax, 4));
+    amax = fmaxf(amax, __shfl_xor_sync(mask16, amax, 8));
+    scale[r] = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+    const ExactDivider div(scale[r]);
+    y[r] = div.y;
+    slow |= div.slow;
+  }
+  if (__any_sync(0xFFFFFFFFu, slow)) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) q[r] = quantise8_e4m3_ieee(raw[r], scale[r]);
+    return;
+  }
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float q0 = __fmul_rn(v[r][e], y[r]);
+      const float rem = __fmaf_rn(-scale[r], q0, v[r][e]);
+      v[r][e] = __fmaf_rn(rem, y[r], q0);
+    }
+    q[r] = make_uint2(pack4_e4m3(v[r][0], v[r][1], v[r][2], v[r][3]), pack4_e4m3(v[r][4], v[r][5], v[r][6], v[r][7]));
+  }
+}
+
+// The exchange at the end of the weight-lane kernel is the epilogue warps' business (it needs their registers);
+// every other warp only takes part in its CTA-wide and cluster-wide barriers, in the same order.
+__device__ __forceinline__ void weight_lane_keep_barriers() {
+  __syncthreads();      // main loop over: the epilogue may overwrite the pipeline stages
+  cluster_sync_all();   // partial tiles visible cluster-wide
+  cluster_sync_all();   // all peers have read them
+}
+
+// Scale loader of the unfused weight-lane kernel (one warp).
+template <int TOK, bool FUSED>
+__device__ __forceinline__ void weight_lane_scale_loader(const WeightLaneParams& p, PipeBars* bars, float* sc,
+                                                         const AbortCtl& ac, int lane, int n_t, int m0, int m_count,
+                                                         int kt0, int nkt) {
+  using C = WeightLane<TOK, FUSED>;
     // ------------------------------ scale loader ------------------------------
     // sc[b][c] = sx[kt, m0+c] * sw[n_t, kt] for the K-tile that accumulator b will hold; second
     // arrival on the accumulator's "full" barrier.  Factors are fetched kScalePrefetch K-tiles ahead.
@@ -1094,14 +1070,244 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         if (i + P < nkt) fetch(i + P, fx[j], fw[j]);
       }
     }
-  } else if (warp >= C::kFirstEpiWarp) {
+}
+
+// grid = (ceil(N/128), splits, ceil(M/TOK)), cluster = (1, splits, 1).
+template <int TOK, bool FUSED>
+__global__ void __launch_bounds__(WeightLane<TOK, FUSED>::kThreads, WeightLane<TOK, FUSED>::kMinCtas)
+weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                   const WeightLaneParams p) {
+  using C = WeightLane<TOK, FUSED>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align_1024(smem_raw);
+  float* sc = reinterpret_cast<float*>(smem + C::kPipeBytes);             // [kNumAcc][TOK] scale products
+  PipeBars* bars = reinterpret_cast<PipeBars*>(smem + C::kPipeBytes + C::kScaleBytes);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int n_t = blockIdx.x;
+  const int z = blockIdx.y;
+  const int m0 = blockIdx.z * TOK;
+  const int m_count = min(p.M - m0, TOK);
+  const int n_umma = (m_count + 15) & ~15;                // tokens padded to the UMMA N granularity
+  const int KT = (p.K + kTileK - 1) / kTileK;
+  const int kt0 = static_cast<int>((static_cast<int64_t>(z) * KT) / p.splits);
+  const int kt1 = static_cast<int>((static_cast<int64_t>(z + 1) * KT) / p.splits);
+  const int nkt = kt1 - kt0;
+  const uint32_t stage_tx = FUSED ? kLaneTileBytes : kLaneTileBytes + p.tok_box * kTileK;
+  const int pre = min(nkt, C::kStages);                   // weight tiles requested before anything else
+  NQ_WL_STAMP(0)
+
+  if (threadIdx.x == 0) {
+    // a stage is full when the weight tile has landed (and, fused, its quantiser warp has written the activations);
+    // an accumulator is full when its UMMAs are complete and its scale products are in shared memory
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(&bars->full[s], FUSED ? 2 : 1); mbar_init(&bars->empty[s], 1); }
+    for (int b = 0; b < C::kNumAcc; ++b) {
+      mbar_init(&bars->tmem_full[b], 2);
+      mbar_init(&bars->tmem_empty[b], C::kEpiWarps);
+    }
+    mbar_init(&bars->teardown, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_w);
+    if (!FUSED) tma_prefetch_desc(&tm_x);
+    // This thread is also the TMA producer.  Weights never depend on the preceding launch, so the first
+    // ring of weight tiles is requested right here - before the CTA-wide barrier, the TMEM allocation and
+    // the dependency wait - to shorten the time from launch to the first byte.
+    const uint64_t stream_once = l2_policy_evict_first();
+    for (int i = 0; i < pre; ++i) {
+      mbar_arrive_expect_tx(&bars->full[i], stage_tx);
+      tma_load_2d_hint(smem + i * C::kStageBytes, &tm_w, &bars->full[i], (kt0 + i) * kTileK, n_t * 128, stream_once);
+    }
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, C::kTmemCols); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  const AbortCtl ac{&bars->abort_flag, p.status, p.wait_limit_ns, p.wait_mode};
+  pdl_launch_next();
+
+  float acc[C::kCols];
+  const int q = warp & 3;
+  const int h = (warp >= C::kFirstEpiWarp && warp < C::kFirstEpiWarp + C::kEpiWarps) ? ((warp - C::kFirstEpiWarp) >> 2) : 0;   // column half (TOK == 256 only)
+  const int col0 = h * C::kCols;
+  bool epi_ok = true;
+
+  if (warp < C::kFirstEpiWarp) {
+   if (C::kTradeRegs) setmaxnreg_dec<C::kRegsLow>();
+   if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    // The first ring of weight tiles is already in flight (requested during set-up); the activation
+    // tiles of those stages follow after the dependency wait.
+    if (lane == 0) {
+      const uint64_t stream_once = l2_policy_evict_first();
+      if (!FUSED) {
+        pdl_wait_prior();
+        for (int i = 0; i < pre; ++i)
+          tma_load_2d(smem + i * C::kStageBytes + kLaneTileBytes, &tm_x, &bars->full[i], (kt0 + i) * kTileK, m0);
+      }
+      bool ok = true;
+      int i = pre;
+      for (; i < nkt; ++i) {
+        const int s = i % C::kStages;
+        const uint32_t ph = (i / C::kStages) & 1;
+        if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteWeightLane + kSiteProdEmpty, i)) { ok = false; break; }
+        uint8_t* a = smem + s * C::kStageBytes;
+        mbar_arrive_expect_tx(&bars->full[s], stage_tx);
+        tma_load_2d_hint(a, &tm_w, &bars->full[s], (kt0 + i) * kTileK, n_t * 128, stream_once);
+        if (!FUSED) tma_load_2d(a + kLaneTileBytes, &tm_x, &bars->full[s], (kt0 + i) * kTileK, m0);
+      }
+      if (!ok) drain_after_abort(bars, C::kStages, static_cast<uint32_t>(i));
+    }
+   } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_e4m3_f32(128, n_umma);
+      bool ok = true;
+      for (int i = 0; i < nkt; ++i) {
+        const int b = i % C::kNumAcc;
+        const uint32_t aph = (i / C::kNumAcc) & 1;
+        if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteWeightLane + kSiteMmaTmemEmpty, i)) { ok = false; break; }
+        const int s = i % C::kStages;
+        const uint32_t ph = (i / C::kStages) & 1;
+        if (!mbar_wait(&bars->full[s], ph, ac, kSiteWeightLane + kSiteMmaFull, i)) { ok = false; break; }
+        if (i == 0) { NQ_WL_STAMP(1) }
+        if (i == nkt - 1) { NQ_WL_STAMP(2) }
+        NQ_QTRACE(5, i)
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
+        const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
+        const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
+        const uint32_t d = tmem_base + b * TOK;
+#pragma unroll
+        for (int k = 0; k < kTileK / 32; ++k)
+          umma_f8(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+        umma_commit(&bars->empty[s]);
+        umma_commit(&bars->tmem_full[b]);
+      }
+      if (!ok) {
+        umma_commit(&bars->teardown);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&bars->teardown, 0) && clock64() - t0 < 40000000ll) {}
+      }
+    }
+   } else if (!FUSED && warp == 2) {
+    weight_lane_scale_loader<TOK, FUSED>(p, bars, sc, ac, lane, n_t, m0, m_count, kt0, nkt);
+   }
+   __syncwarp();
+   weight_lane_keep_barriers();
+  } else if (FUSED && warp >= C::kFirstQuantWarp) {
+    // ------------------------------ activation quantisers ---------------------
+    // Four warps turn the bf16 activations into the e4m3 operand tiles in shared memory (same arithmetic as
+    // act_quant_kernel, so the bytes are identical) and into the scale products of the accumulators.  Warp w
+    // owns K-tiles w, w + 4, ...: a conversion is one long dependency chain (amax -> scale -> reciprocal ->
+    // quotients -> pack), so four tiles in flight matter more than four warps on one tile.  Inside a tile, 16
+    // lanes serve a token row (8 elements each), two rows per warp instruction, up to four row pairs (a unit)
+    // converted together; two units are held in registers and the loads of the unit after next are issued as
+    // soon as a unit has been converted.
+    setmaxnreg_inc<C::kRegsQuant>();
+    const int qw = warp - C::kFirstQuantWarp;              // 0..3
+    const int sub = lane >> 4, j = lane & 15;
+    const uint32_t mask16 = 0xFFFFu << (lane & 16);
+    const float* sw_row = p.sw + static_cast<int64_t>(n_t) * p.ld_sw;
+    const int npairs = (m_count + 1) >> 1;                 // row pairs that hold a token
+    const int upt = (npairs + 3) >> 2;                     // units per tile
+    struct Cursor { int i, hh; };                          // K-tile (relative to kt0) and unit inside it
+    auto advance = [&](Cursor& c) { if (++c.hh == upt) { c.hh = 0; c.i += C::kQuantWarps; } };
+    auto pairs_in = [&](int hh) { const int c = min(4, npairs - 4 * hh); return c == 3 ? 4 : c; };   // 1, 2 or 4
+    auto row_of = [&](int hh, int r) { return (hh * 4 + r) * 2 + sub; };
+    pdl_wait_prior();                                       // x comes from the preceding launch
+    uint4 raw[2][4];
+    auto fetch = [&](const Cursor& c, uint4 (&dst)[4]) {
+      // addresses are clamped into the matrix and the surplus is masked when the values are used: an
+      // unconditional load does not have to be waited for before the next instruction
+      const int k = min((kt0 + c.i) * kTileK + j * 8, p.K - 8);
+      const int n = pairs_in(c.hh);
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        if (r < n)
+          dst[r] = ld_global_v4_pinned(p.x + static_cast<int64_t>(m0 + min(row_of(c.hh, r), m_count - 1)) * p.ldx + k);
+    };
+    Cursor cur{qw, 0}, pf{qw, 0};
+    if (pf.i < nkt) { fetch(pf, raw[0]); advance(pf); }
+    if (pf.i < nkt) { fetch(pf, raw[1]); advance(pf); }
+    bool ok = true;
+    float sw_tile = 0.0f;
+    while (ok && cur.i < nkt) {
+#pragma unroll
+      for (int ub = 0; ub < 2; ++ub) {
+        if (cur.i >= nkt) break;
+        const int i = cur.i, hh = cur.hh;
+        const int s = i % C::kStages;
+        const int b = i % C::kNumAcc;
+        uint8_t* tile = smem + s * C::kStageBytes + kLaneTileBytes;
+        if (hh == 0) {
+          sw_tile = ld_global_f32_pinned(sw_row + kt0 + i);
+          const uint32_t ph = (i / C::kStages) & 1;
+          const uint32_t aph = (i / C::kNumAcc) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteWeightLane + kSiteProdEmpty, i) ||
+              !mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteWeightLane + kSiteScaleEmpty, i)) { ok = false; break; }
+          if (lane == 0) { NQ_QTRACE(0, i) }
+          if (i < (C::kStages > C::kNumAcc ? C::kStages : C::kNumAcc)) {
+            // rows between the last token pair and the UMMA's N extent: zeros, written on the first pass over the rings
+            for (int pz = npairs; pz * 2 < n_umma; ++pz) {
+              const int row = pz * 2 + sub;
+              *reinterpret_cast<uint2*>(tile + row * 128 + (((j >> 1) ^ (row & 7)) << 4) + (j & 1) * 8) = make_uint2(0u, 0u);
+              if (j == 0) sc[b * TOK + row] = 0.0f;
+            }
+          }
+        }
+        const bool k_in = (kt0 + i) * kTileK + j * 8 < p.K;
+        auto convert = [&](auto nr_tag) {
+          constexpr int NR = decltype(nr_tag)::value;
+          uint4 in[NR];
+          uint2 out[NR];
+          float scale[NR];
+#pragma unroll
+          for (int r = 0; r < NR; ++r) {
+            const uint32_t keep = (k_in && row_of(hh, r) < m_count) ? 0xFFFFFFFFu : 0u;
+            in[r] = make_uint4(raw[ub][r].x & keep, raw[ub][r].y & keep, raw[ub][r].z & keep, raw[ub][r].w & keep);
+          }
+          quantise_rows_e4m3<NR>(in, mask16, out, scale);
+#pragma unroll
+          for (int r = 0; r < NR; ++r) {
+            const int row = row_of(hh, r);
+            // K-major tile with 128-byte swizzle: 16-byte chunk c of row r lives at chunk c ^ (r & 7)
+            *reinterpret_cast<uint2*>(tile + row * 128 + (((j >> 1) ^ (row & 7)) << 4) + (j & 1) * 8) = out[r];
+            if (j == 0) sc[b * TOK + row] = scale[r] * sw_tile;
+          }
+        };
+        const int n = pairs_in(hh);
+        if (n == 4) convert(std::integral_constant<int, 4>{});
+        else if (n == 2) convert(std::integral_constant<int, 2>{});
+        else convert(std::integral_constant<int, 1>{});
+        if (hh == upt - 1) {
+          if (lane == 0) { NQ_QTRACE(1, i) }
+          fence_proxy_async_smem();                         // generic-proxy writes -> visible to the tensor core
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(&bars->full[s]);
+            mbar_arrive(&bars->tmem_full[b]);
+            NQ_QTRACE(2, i)
+          }
+        }
+        advance(cur);
+        if (pf.i < nkt) { fetch(pf, raw[ub]); advance(pf); }
+      }
+    }
+    __syncwarp();
+    weight_lane_keep_barriers();
+  } else if (warp >= C::kFirstEpiWarp && warp < C::kFirstEpiWarp + C::kEpiWarps) {
     // ------------------------------ epilogue ----------------------------------
+    if (C::kTradeRegs) setmaxnreg_inc<C::kRegsHigh>();
 #pragma unroll
     for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
     for (int i = 0; i < nkt; ++i) {
       const int b = i % C::kNumAcc;
       const uint32_t aph = (i / C::kNumAcc) & 1;
       if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteWeightLane + kSiteEpiTmemFull, i)) { epi_ok = false; break; }
+      if (threadIdx.x == 128) { NQ_QTRACE(3, i) }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * TOK + col0;
       const float* scb = sc + b * TOK + col0;
@@ -1123,88 +1329,89 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
+      if (threadIdx.x == 128) { NQ_QTRACE(4, i) }
     }
-  }
 
-  // All MMAs of this CTA have completed (the epilogue waited for the last
-  // accumulator), so the pipeline stages are free: reuse them for the exchange.
-  NQ_WL_STAMP(3)
-  __syncthreads();
-  NQ_WL_STAMP(4)
-  float* xch = reinterpret_cast<float*>(smem);              // [TOK][128] fp32, weight row fastest
-  if (warp >= C::kFirstEpiWarp) {
-    const int nrow = q * 32 + lane;
-#pragma unroll
-    for (int c = 0; c < C::kCols; ++c)
-      if (col0 + c < n_umma) xch[(col0 + c) * 128 + nrow] = epi_ok ? acc[c] : 0.0f;
-  }
-  cluster_sync_all();   // partial tiles of all splits are visible cluster-wide
-  NQ_WL_STAMP(5)
+    // All MMAs of this CTA have completed (the epilogue waited for the last
+    // accumulator), so the pipeline stages are free: reuse them for the exchange.
+    NQ_WL_STAMP(3)
+    __syncthreads();
+    NQ_WL_STAMP(4)
+    float* xch = reinterpret_cast<float*>(smem);              // [TOK][128] fp32, weight row fastest
+    {
+      const int nrow = q * 32 + lane;
+  #pragma unroll
+      for (int c = 0; c < C::kCols; ++c)
+        if (col0 + c < n_umma) xch[(col0 + c) * 128 + nrow] = epi_ok ? acc[c] : 0.0f;
+    }
+    cluster_sync_all();   // partial tiles of all splits are visible cluster-wide
+    NQ_WL_STAMP(5)
 
-  if (warp >= C::kFirstEpiWarp && bars->abort_flag == 0) {
-    // This CTA sums tokens z, z+splits, ... over all splits in rank order (fixed
-    // order => bit-identical results run to run), adds the bias and writes y.
-    const uint32_t my_rank = cluster_ctarank();
-    const int et = threadIdx.x - 32 * C::kFirstEpiWarp;
-    const int nq4 = et & 31;                               // which 4 weight rows
-    const int n = n_t * 128 + nq4 * 4;
-    auto finish_row = [&](int mi, float4 sum) {
-      if (n >= p.N) return;
-      float v[4] = {sum.x, sum.y, sum.z, sum.w};
-      if (p.bias != nullptr) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
-      }
-      __nv_bfloat16* yp = p.y + static_cast<int64_t>(m0 + mi) * p.ldy + n;
-      if (p.y_vec && n + 4 <= p.N) {
-        uint2 o;
-        o.x = pack_bf16x2(v[0], v[1]);
-        o.y = pack_bf16x2(v[2], v[3]);
-        *reinterpret_cast<uint2*>(yp) = o;
+    if (bars->abort_flag == 0) {
+      // This CTA sums tokens z, z+splits, ... over all splits in rank order (fixed
+      // order => bit-identical results run to run), adds the bias and writes y.
+      const uint32_t my_rank = cluster_ctarank();
+      const int et = threadIdx.x - 32 * C::kFirstEpiWarp;
+      const int nq4 = et & 31;                               // which 4 weight rows
+      const int n = n_t * 128 + nq4 * 4;
+      auto finish_row = [&](int mi, float4 sum) {
+        if (n >= p.N) return;
+        float v[4] = {sum.x, sum.y, sum.z, sum.w};
+        if (p.bias != nullptr) {
+  #pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
+        }
+        __nv_bfloat16* yp = p.y + static_cast<int64_t>(m0 + mi) * p.ldy + n;
+        if (p.y_vec && n + 4 <= p.N) {
+          uint2 o;
+          o.x = pack_bf16x2(v[0], v[1]);
+          o.y = pack_bf16x2(v[2], v[3]);
+          *reinterpret_cast<uint2*>(yp) = o;
+        } else {
+  #pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (n + i < p.N) yp[i] = __float2bfloat16_rn(v[i]);
+        }
+      };
+      const int tok_stride = p.splits * C::kEpiWarps;
+      const int mi_first = static_cast<int>(my_rank) + (et >> 5) * p.splits;
+      if (p.splits == 1) {
+        // no peers: plain reads of this CTA's own tile (the compiler pipelines them)
+  #pragma unroll 4
+        for (int mi = mi_first; mi < m_count; mi += tok_stride)
+          finish_row(mi, *reinterpret_cast<const float4*>(xch + mi * 128 + nq4 * 4));
       } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (n + i < p.N) yp[i] = __float2bfloat16_rn(v[i]);
-      }
-    };
-    const int tok_stride = p.splits * C::kEpiWarps;
-    const int mi_first = static_cast<int>(my_rank) + (et >> 5) * p.splits;
-    if (p.splits == 1) {
-      // no peers: plain reads of this CTA's own tile (the compiler pipelines them)
-#pragma unroll 4
-      for (int mi = mi_first; mi < m_count; mi += tok_stride)
-        finish_row(mi, *reinterpret_cast<const float4*>(xch + mi * 128 + nq4 * 4));
-    } else {
-      // Remote loads are slow one at a time: keep eight in flight (8 / splits token rows per pass),
-      // then add them up in rank order.
-      const int rows_per_pass = p.splits >= 8 ? 1 : 8 / p.splits;
-      for (int mi = mi_first; mi < m_count; mi += tok_stride * rows_per_pass) {
-        float4 part[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int t = j / p.splits, r = j - t * p.splits;
-          const int row = mi + t * tok_stride;
-          if (t < rows_per_pass && row < m_count)
-            part[j] = ld_dsmem_f4(smem_u32(xch + row * 128 + nq4 * 4), static_cast<uint32_t>(r));
-        }
-        for (int t = 0; t < rows_per_pass; ++t) {
-          const int row = mi + t * tok_stride;
-          if (row >= m_count) break;
-          float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
+        // Remote loads are slow one at a time: keep eight in flight (8 / splits token rows per pass),
+        // then add them up in rank order.
+        const int rows_per_pass = p.splits >= 8 ? 1 : 8 / p.splits;
+        for (int mi = mi_first; mi < m_count; mi += tok_stride * rows_per_pass) {
+          float4 part[8];
+  #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const int tj = j / p.splits;
-            if (tj == t) { sum.x += part[j].x; sum.y += part[j].y; sum.z += part[j].z; sum.w += part[j].w; }
+            const int t = j / p.splits, r = j - t * p.splits;
+            const int row = mi + t * tok_stride;
+            if (t < rows_per_pass && row < m_count)
+              part[j] = ld_dsmem_f4(smem_u32(xch + row * 128 + nq4 * 4), static_cast<uint32_t>(r));
           }
-          finish_row(row, sum);
+          for (int t = 0; t < rows_per_pass; ++t) {
+            const int row = mi + t * tok_stride;
+            if (row >= m_count) break;
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int tj = j / p.splits;
+              if (tj == t) { sum.x += part[j].x; sum.y += part[j].y; sum.z += part[j].z; sum.w += part[j].w; }
+            }
+            finish_row(row, sum);
+          }
         }
       }
     }
+    NQ_WL_STAMP(6)
+    cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
+    NQ_WL_STAMP(7)
   }
-  NQ_WL_STAMP(6)
-  cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
-  NQ_WL_STAMP(7)
 
   tc_fence_before_sync();
   __syncthreads();
@@ -1346,16 +1553,18 @@ int run_token_pair(const GemmArgs& a, DeviceCtx* ctx) {
   return check_cuda(e);
 }
 
-template <int TOK>
+template <int TOK, bool FUSED = false>
 int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
-  using C = WeightLane<TOK>;
+  using C = WeightLane<TOK, FUSED>;
   const int tokens_box = static_cast<int>(a.M >= TOK ? TOK : ((a.M + 15) / 16) * 16);
   CUtensorMap tm_x, tm_w;
   int st = make_tmap_u8_2d(&tm_w, a.wq, a.N, a.K, a.ld_wq, 128);
   if (st != NQ_OK) return st;
-  st = make_tmap_u8_2d(&tm_x, a.xq, a.M, a.K, a.ld_xq, tokens_box);
+  if (FUSED) tm_x = tm_w;                                   // unused by the fused kernel
+  else st = make_tmap_u8_2d(&tm_x, a.xq, a.M, a.K, a.ld_xq, tokens_box);
   if (st != NQ_OK) return st;
   WeightLaneParams p;
+  p.x = static_cast<const __nv_bfloat16*>(a.x); p.ldx = a.ldx;
   p.sx = a.sx; p.ld_sx = a.ld_sx; p.sw = a.sw; p.ld_sw = a.ld_sw;
   p.bias = static_cast<const __nv_bfloat16*>(a.bias);
   p.y = static_cast<__nv_bfloat16*>(a.y); p.ldy = a.ldy;
@@ -1369,7 +1578,7 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
   p.wait_limit_ns = wait_limit_ns();
   dim3 grid(static_cast<unsigned>((a.N + 127) / 128), static_cast<unsigned>(splits),
             static_cast<unsigned>((a.M + TOK - 1) / TOK));
-  cudaError_t e = launch_ex(weight_lane_kernel<TOK>, grid, dim3(C::kThreads), C::kSmemBytes, a.stream, splits, a.pdl,
+  cudaError_t e = launch_ex(weight_lane_kernel<TOK, FUSED>, grid, dim3(C::kThreads), C::kSmemBytes, a.stream, splits, a.pdl,
                             tm_w, tm_x, p);
   count_launch();
   return check_cuda(e);
@@ -1419,6 +1628,10 @@ int launch_gemm_weight_lane(const GemmArgs& a, DeviceCtx* ctx) {
     while (s * 2 <= splits) s *= 2;
     splits = s;
   }
+  if (a.x != nullptr) {                                      // quantise inside the GEMM (decode batches)
+    if (a.M <= 32) return run_weight_lane<32, true>(a, ctx, splits);
+    return NQ_ERR_UNSUPPORTED;
+  }
   if (a.M <= 32) return run_weight_lane<32>(a, ctx, splits);
   if (a.M <= 64) return run_weight_lane<64>(a, ctx, splits);
   if (a.M <= 128) return run_weight_lane<128>(a, ctx, splits);
@@ -1435,10 +1648,11 @@ int setup_gemm_kernels() {
   NQ_SET_SMEM(token_lane_kernel<128>, TokenLane<128>::kSmemBytes)
   NQ_SET_SMEM(token_lane_kernel<192>, TokenLane<192>::kSmemBytes)
   NQ_SET_SMEM(token_lane_kernel<256>, TokenLane<256>::kSmemBytes)
-  NQ_SET_SMEM(weight_lane_kernel<32>, WeightLane<32>::kSmemBytes)
-  NQ_SET_SMEM(weight_lane_kernel<64>, WeightLane<64>::kSmemBytes)
-  NQ_SET_SMEM(weight_lane_kernel<128>, WeightLane<128>::kSmemBytes)
-  NQ_SET_SMEM(weight_lane_kernel<256>, WeightLane<256>::kSmemBytes)
+  NQ_SET_SMEM((weight_lane_kernel<32, false>), (WeightLane<32>::kSmemBytes))
+  NQ_SET_SMEM((weight_lane_kernel<64, false>), (WeightLane<64>::kSmemBytes))
+  NQ_SET_SMEM((weight_lane_kernel<128, false>), (WeightLane<128>::kSmemBytes))
+  NQ_SET_SMEM((weight_lane_kernel<256, false>), (WeightLane<256>::kSmemBytes))
+  NQ_SET_SMEM((weight_lane_kernel<32, true>), (WeightLane<32, true>::kSmemBytes))
 #undef NQ_SET_SMEM
   return NQ_OK;
 }

@@ -31,6 +31,7 @@ int launch_weight_quant(const void* w, int64_t N, int64_t K, int64_t ldw, void* 
                         int64_t ld_sw, cudaStream_t stream);
 
 struct GemmArgs {
+  const void* x = nullptr; int64_t ldx = 0;   // unquantised bf16 activations: set only for the fused decode path
   const void* xq; int64_t ld_xq;
   const float* sx; int64_t ld_sx;
   const void* wq; int64_t ld_wq;

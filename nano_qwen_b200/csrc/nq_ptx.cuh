@@ -373,4 +373,47 @@ __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[16]) {
       : "memory");
 }
 
+// Global loads that stay where they are written.  A compiler under register pressure may move an ordinary (or
+// __ldg) load down to its first use, which turns a software prefetch into an exposed round trip; a volatile asm
+// statement keeps its place among the other volatile asm statements (barrier waits, arrivals).
+__device__ __forceinline__ uint4 ld_global_v4_pinned(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float ld_global_f32_pinned(const float* p) {
+  float v;
+  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
+// ------------------------- quantisation arithmetic (shared by the quantiser kernels and the fused GEMM) ---
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+
+// x / s, correctly rounded, for many x and one s.  With y = RN(1/s): q0 = RN(x*y), r = x - s*q0 (exact in one
+// FMA), q = RN(q0 + r*y) equals RN(x/s) unless the significand of s is all ones or an exponent is extreme
+// (Markstein); those scales take the IEEE divide.  Three instructions per element instead of about ten.
+struct ExactDivider {
+  float s, y;
+  bool slow;
+  __device__ __forceinline__ explicit ExactDivider(float scale) : s(scale) {
+    const uint32_t bits = __float_as_uint(scale);
+    slow = !(scale >= 1e-30f && scale <= 1e30f) || ((bits & 0x7FFFFFu) == 0x7FFFFFu);
+    y = __frcp_rn(scale);
+  }
+  __device__ __forceinline__ float operator()(float x) const {
+    if (slow) return __fdiv_rn(x, s);
+    const float q0 = __fmul_rn(x, y);
+    const float r = __fmaf_rn(-s, q0, x);
+    return __fmaf_rn(r, y, q0);
+  }
+};
+
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+
 }  // namespace nq

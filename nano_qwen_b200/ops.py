@@ -11,7 +11,8 @@ import torch
 
 from . import _cabi
 from ._cabi import (ALGO_AUTO, ALGO_TOKEN_LANE, ALGO_TOKEN_LANE_128, ALGO_TOKEN_LANE_192,  # noqa: F401  (re-exported)
-                    ALGO_TOKEN_LANE_256, ALGO_TOKEN_PAIR, ALGO_TOKEN_PAIR_128, ALGO_WEIGHT_LANE)
+                    ALGO_TOKEN_LANE_256, ALGO_TOKEN_PAIR, ALGO_TOKEN_PAIR_128, ALGO_WEIGHT_LANE,
+                    ALGO_WEIGHT_LANE_FUSED)
 
 GROUP = 128
 FP8 = torch.float8_e4m3fn
@@ -162,12 +163,17 @@ def fp8_linear(x: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, bias: torch.
     if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_contiguous()):
         bias = bias.to(torch.bfloat16).contiguous()
     G = (K + GROUP - 1) // GROUP
-    xq = torch.empty((M, _round_up(K, 16)), dtype=FP8, device=x.device)
-    sx = torch.empty((G, _round_up(M, 4)), dtype=torch.float32, device=x.device)
+    ldx = x2.stride(0) if M > 1 else max(K, x2.stride(0))
+    # Decode batches that the library quantises inside the GEMM kernel need no scratch (same rule as the library's;
+    # if the two ever disagreed the call would be rejected for its null scratch, not miscomputed).
+    limit = {ALGO_AUTO: _cabi.FUSED_AUTO_TOKENS, ALGO_WEIGHT_LANE_FUSED: _cabi.FUSED_MAX_TOKENS}.get(algo, 0)
+    fused = M <= limit and K % 8 == 0 and ldx % 8 == 0 and x2.data_ptr() % 16 == 0
+    xq = None if fused else torch.empty((M, _round_up(K, 16)), dtype=FP8, device=x.device)
+    sx = None if fused else torch.empty((G, _round_up(M, 4)), dtype=torch.float32, device=x.device)
     st = _cabi.lib().nq_fp8_linear(
-        x2.data_ptr(), x2.stride(0) if M > 1 else max(K, x2.stride(0)),
+        x2.data_ptr(), ldx,
         wq.data_ptr(), wq.stride(0) if N > 1 else _round_up(K, 16), sw.data_ptr(), sw.stride(0) if sw.shape[0] > 1 else G,
         bias.data_ptr() if bias is not None else None, y.data_ptr(), y.stride(0) if M > 1 else N, M, N, K,
-        xq.data_ptr(), sx.data_ptr(), None, 0, algo, split_k, _stream())
+        None if fused else xq.data_ptr(), None if fused else sx.data_ptr(), None, 0, algo, split_k, _stream())
     _cabi.check(st, "nq_fp8_linear")
     return y if out is not None else y.view(*lead, N)
