@@ -43,6 +43,21 @@ FLOPS_PER_TOKEN_LAYER = 2 * (HIDDEN * (HEADS + 2 * KV_HEADS) * HEAD_DIM + HIDDEN
 KINDS = ("qkv", "o_proj", "gate_up", "down")
 
 
+# DRAM traffic of the dominant kernel: one ncu capture of its qkv launch at M = 8192 (profiles/
+# token_lane_kernel_qkv_M8192.md) read 77.7 MB and wrote 70.6 MB for 159.4 MB of algorithmic bytes (e4m3 x, e4m3 W,
+# bf16 y); the other three shapes of the pass are scaled by the same ratio (operands are read once, y is written once).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 148.3 / 159.4
+
+
+def prefill_gemm_traffic_bytes(layers) -> float:
+    """dram read + write bytes per launch of the prefill-pass GEMM, averaged over one rank's four shapes."""
+    total = 0.0
+    for name in KINDS:
+        n, k = layers[0][name].weight.shape
+        total += M_PREFILL * k + n * k + 2.0 * M_PREFILL * n
+    return total / len(KINDS) * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE
+
+
 def flops_per_step() -> float:
     return float(LAYERS) * FLOPS_PER_TOKEN_LAYER * (M_DECODE + M_PREFILL)
 
@@ -391,7 +406,9 @@ def run_gpu_arm(args) -> None:
                          "peak_note": f"2 x bf16_tflops_sustained of {peaks['source']} (the e4m3 UMMA rate is twice the "
                                       "bf16 rate); torch._scaled_mm per-tensor FP8 measured 3046 burst / 2618 sustained here",
                          "launches": n_gemm, "avg_launch_us": ms_gemm * 1e3 / max(n_gemm, 1),
-                         "traffic": None},
+                         "traffic": prefill_gemm_traffic_bytes(layers), "traffic_unit": "bytes per launch",
+                         "traffic_note": "ncu dram read+write of the qkv launch (148.3 MB for 159.4 MB algorithmic) "
+                                         "scaled to the mean of the four shapes of the pass"},
             "passes": {"decode_ms": ms_decode, "prefill_ms": ms_prefill, "prefill_gemm_only_ms": ms_gemm,
                        "decode_gemm_only_ms": ms_dec_gemm,
                        "decode_layer_us": ms_decode * 1e3 / LAYERS, "prefill_layer_us": ms_prefill * 1e3 / LAYERS,
