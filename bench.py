@@ -183,21 +183,27 @@ class ClockSampler:
                 "power_w_max": max(power), "samples": len(sm)}
 
 
-def build_stack(L, ops, tp_rank: int, tp_size: int):
-    """36 x 4 drop-in layers on the current device with random-init FP8 weights (this rank's shards)."""
+# Qwen3-32B-shaped layer (config 4 of the contract): hidden, heads, kv heads, head dim, intermediate
+DIMS_32B = (5120, 64, 8, 128, 25600)
+
+
+def build_stack(L, ops, tp_rank: int, tp_size: int, n_layers: int = LAYERS,
+                dims=(HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER), seed_base: int = 0):
+    """n_layers x 4 drop-in layers on the current device with random-init FP8 weights (this rank's shards)."""
+    hidden, heads, kv_heads, head_dim, inter = dims
     torch.set_default_device("cuda")
     torch.set_default_dtype(torch.bfloat16)
     try:
         layers = []
-        for li in range(LAYERS):
+        for li in range(n_layers):
             layer = {
-                "qkv": L.QKVParallelLinear(HIDDEN, HEAD_DIM, HEADS, KV_HEADS),
-                "o_proj": L.RowParallelLinear(HIDDEN, HIDDEN),
-                "gate_up": L.MergedColumnParallelLinear(HIDDEN, [INTER, INTER]),
-                "down": L.RowParallelLinear(INTER, HIDDEN),
+                "qkv": L.QKVParallelLinear(hidden, head_dim, heads, kv_heads),
+                "o_proj": L.RowParallelLinear(heads * head_dim, hidden),
+                "gate_up": L.MergedColumnParallelLinear(hidden, [inter, inter]),
+                "down": L.RowParallelLinear(inter, hidden),
             }
             for ki, (name, mod) in enumerate(layer.items()):
-                gen = torch.Generator(device="cuda").manual_seed(1000 * li + 10 * ki + tp_rank)
+                gen = torch.Generator(device="cuda").manual_seed(seed_base + 1000 * li + 10 * ki + tp_rank)
                 n, k = mod.weight.shape
                 w = (torch.randn(n, k, generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
                 wq, sw = ops.weight_quant(w)          # this rank's shard, quantised on the device
@@ -370,6 +376,43 @@ def run_gpu_arm(args) -> None:
             }
             del xs
         torch.cuda.synchronize()
+        # ---- config 4: one Qwen3-32B-shaped layer at this TP degree (three copies of the weights are cycled so that
+        #      they never come from L2), M = 1 and 64 from a CUDA graph, M = 8192 eager ----
+        hid32, heads32, kv32, hd32, inter32 = DIMS_32B
+        big = build_stack(L, ops, rank, tp, n_layers=3, dims=DIMS_32B, seed_base=777000)
+        flops32 = 2 * (hid32 * (heads32 + 2 * kv32) * hd32 + heads32 * hd32 * hid32 + hid32 * 2 * inter32 + inter32 * hid32)
+        shapes32 = {"qkv": (hid32, (heads32 + 2 * kv32) * hd32 // tp), "o_proj": (heads32 * hd32 // tp, hid32),
+                    "gate_up": (hid32, 2 * inter32 // tp), "down": (inter32 // tp, hid32)}
+        detail["layer_32b"] = {}
+        for m in (1, 64, 8192):
+            xs = {name: torch.randn((m, k), generator=gen_d, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+                  for name, (k, n) in shapes32.items()}
+            if m <= 64:
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    run_pass(big[:1], xs)
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                gm = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gm):
+                    for _ in range(4):
+                        run_pass(big, xs)
+                ms, _ = timed(gm.replay, 5, 2)
+                layer_us = ms * 1e3 / (4 * len(big))
+                del gm
+            else:
+                ms, _ = timed(lambda: run_pass(big, xs), 2, 1)
+                layer_us = ms * 1e3 / len(big)
+            bytes_layer = sum(2 * m * k + n * k + 4 * ((n + 127) // 128) * ((k + 127) // 128) + 2 * m * n
+                              for k, n in shapes32.values())
+            detail["layer_32b"][str(m)] = {
+                "layer_us": round(layer_us, 2),
+                "tflops": round(flops32 * m / (layer_us * 1e-6) / 1e12, 1),
+                "hbm_gbs_per_gpu": round(bytes_layer / (layer_us * 1e-6) / 1e9, 1),
+            }
+            del xs
+        del big
+        torch.cuda.synchronize()
     status = _cabi.device_status()
 
     if rank == 0:
@@ -415,7 +458,8 @@ def run_gpu_arm(args) -> None:
                        "decode_hbm_gbs": decode_gbs, "decode_hbm_frac_of_measured": decode_gbs / peaks["hbm_gbs"],
                        "prefill_tflops": LAYERS * FLOPS_PER_TOKEN_LAYER * M_PREFILL / (ms_prefill * 1e-3) / 1e12},
             "detail": {"note": "one pass of the same stack per batch size M: act quant + GEMM (+ all-reduce) per linear; "
-                               "layer_us = pass time / 36; hbm_gbs_per_gpu uses the algorithmic bytes of one rank's layer "
+                               "layer_us = pass time / 36 (layer_32b: one Qwen3-32B-shaped layer at this TP degree, three "
+                               "weight copies cycled); hbm_gbs_per_gpu uses the algorithmic bytes of one rank's layer "
                                f"(measured copy peak {peaks['hbm_gbs']} GB/s); tflops is the whole job",
                        **detail},
             "device_status": status["code"],

@@ -30,6 +30,7 @@ import torch.distributed as dist
 from torch import nn
 
 from .. import ops
+from . import p2p_reduce
 
 BLOCK = 128
 FP8 = torch.float8_e4m3fn
@@ -196,6 +197,10 @@ class QKVParallelLinear(ColumnParallelLinear):
 class RowParallelLinear(LinearBase):
     """Input features split across ranks; partial outputs summed (reference ``linear.py:131-156``).
 
+    The sum is NCCL's all-reduce, as in the reference, except for decode-sized outputs on an NCCL group of 2..8
+    ranks, which one kernel per rank sums over peer memory (``p2p_reduce``; same result on every rank, fp32
+    accumulation in rank order; ``RowParallelLinear.p2p_reduce = False`` or ``NQ_P2P_REDUCE=0`` keeps NCCL).
+
     Optionally (``overlap_chunks > 1``) the sum is pipelined against the GEMM for prefill-sized batches:
     the token rows are processed in up to ``overlap_chunks`` chunks of at least ``overlap_min_rows``
     rows, and the all-reduce of chunk *i* (NCCL's own stream) runs while the GEMM of chunk *i+1*
@@ -204,6 +209,7 @@ class RowParallelLinear(LinearBase):
     CUDA-graph capture (decode) the call is always a single GEMM + all-reduce, like the reference.
     """
 
+    p2p_reduce = True            # small outputs are summed over peer memory instead of NCCL (see p2p_reduce.py)
     overlap_chunks = 1
     overlap_min_rows = 2048
     overlap_sm_reserve = 16      # SMs the chunk GEMMs leave to the all-reduce kernel that runs beside them
@@ -230,7 +236,11 @@ class RowParallelLinear(LinearBase):
         chunks = min(self.overlap_chunks, rows // self.overlap_min_rows)
         if chunks < 2 or not x.is_cuda or torch.cuda.is_current_stream_capturing():
             y = self._linear(x, bias)
-            dist.all_reduce(y)
+            reducer = p2p_reduce.get_reducer() if (self.p2p_reduce and x.is_cuda) else None
+            if reducer is not None and reducer.fits(y):
+                reducer.reduce_(y)           # decode-sized: one kernel over peer memory
+            else:
+                dist.all_reduce(y)
             return y
         x2 = x.reshape(rows, x.shape[-1])
         y = torch.empty((rows, self.output_size), dtype=torch.bfloat16, device=x.device)

@@ -1,0 +1,111 @@
+"""Row-parallel SUM over peer memory for decode-sized outputs (``nq_row_reduce_p2p``).
+
+Stands in for the ``dist.all_reduce(y)`` that ends the reference's ``RowParallelLinear.forward``
+(``nano_qwen/layers/linear.py:154-155``) when ``y`` is small: NCCL's all-reduce costs a fixed latency per call that
+dominates a 16-512 KiB message, one kernel that pushes the partial to every peer over NVLink and adds what the peers
+pushed does not.  Larger messages keep NCCL (a one-shot exchange moves ``tp - 1`` copies of the message per GPU).
+
+``torch.distributed`` is only the plumbing: it carries the 64-byte IPC handles between the ranks at set-up.
+All ranks must be processes on one node, one GPU each.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import _cabi
+
+_P2P_MAX_BLOCKS = 512          # NQ_P2P_MAX_BLOCKS
+_HANDLE_BYTES = 64             # NQ_P2P_HANDLE_BYTES
+
+
+class P2PRowReducer:
+    """One per process: inbox, flags and call counter of this rank plus the mapped inboxes / flags of the peers."""
+
+    def __init__(self, slot_bytes: int, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.tp = dist.get_world_size(group)
+        if not 2 <= self.tp <= 8:
+            raise ValueError("peer-memory reduction needs 2..8 ranks")
+        self.slot_bytes = (int(slot_bytes) + 255) // 256 * 256
+        lib = _cabi.lib()
+        self._own = []
+        mine = {}
+        for name, size in (("inbox", 2 * self.tp * self.slot_bytes), ("flags", self.tp * _P2P_MAX_BLOCKS * 4),
+                           ("state", 256)):
+            ptr = ctypes.c_void_p()
+            _cabi.check(lib.nq_p2p_alloc(size, ctypes.byref(ptr)), "nq_p2p_alloc")
+            mine[name] = ptr.value
+            self._own.append(ptr.value)
+        handles = {}
+        for name in ("inbox", "flags"):
+            buf = (ctypes.c_ubyte * _HANDLE_BYTES)()
+            _cabi.check(lib.nq_p2p_export(mine[name], buf), "nq_p2p_export")
+            handles[name] = bytes(buf)
+        gathered = [None] * self.tp
+        dist.all_gather_object(gathered, handles, group=group)
+        self._mapped = []
+        ptrs = {"inbox": [], "flags": []}
+        for r in range(self.tp):
+            for name in ("inbox", "flags"):
+                if r == self.rank:
+                    ptrs[name].append(mine[name])
+                    continue
+                raw = (ctypes.c_ubyte * _HANDLE_BYTES).from_buffer_copy(gathered[r][name])
+                ptr = ctypes.c_void_p()
+                _cabi.check(lib.nq_p2p_import(raw, ctypes.byref(ptr)), "nq_p2p_import")
+                ptrs[name].append(ptr.value)
+                self._mapped.append(ptr.value)
+        self._inbox = (ctypes.c_void_p * self.tp)(*ptrs["inbox"])
+        self._flags = (ctypes.c_void_p * self.tp)(*ptrs["flags"])
+        self._state = mine["state"]
+        dist.barrier(group=group)          # every inbox and flag array exists and is zero before anyone pushes
+
+    def fits(self, y: torch.Tensor) -> bool:
+        n = y.numel()
+        return (y.dtype == torch.bfloat16 and y.is_contiguous() and n % 8 == 0 and n * 2 <= self.slot_bytes
+                and y.data_ptr() % 16 == 0)
+
+    def reduce_(self, y: torch.Tensor) -> torch.Tensor:
+        """In-place SUM of ``y`` over the ranks; enqueued on the current stream (capturable)."""
+        st = _cabi.lib().nq_row_reduce_p2p(y.data_ptr(), y.data_ptr(), y.numel(), self._inbox, self._flags, self.rank,
+                                           self.tp, self.slot_bytes, self._state,
+                                           torch.cuda.current_stream().cuda_stream)
+        _cabi.check(st, "nq_row_reduce_p2p")
+        return y
+
+
+_reducer: P2PRowReducer | None = None
+_reducer_failed = False
+
+
+def max_message_bytes(tp: int) -> int:
+    """Largest ``y`` the peer-memory path takes: a one-shot exchange receives ``tp - 1`` messages per GPU, so the
+    limit shrinks with the number of ranks (2 MiB of inbound traffic per call); ``NQ_P2P_REDUCE_MAX_BYTES`` overrides."""
+    env = os.environ.get("NQ_P2P_REDUCE_MAX_BYTES")
+    if env is not None:
+        return int(env)
+    return (2 << 20) // max(tp - 1, 1)
+
+
+def get_reducer() -> P2PRowReducer | None:
+    """The process-wide reducer of the default group, created on first use (a collective call: every rank reaches
+    it in its first row-parallel forward).  ``NQ_P2P_REDUCE=0`` keeps NCCL for every size."""
+    global _reducer, _reducer_failed
+    if _reducer is not None or _reducer_failed:
+        return _reducer
+    if os.environ.get("NQ_P2P_REDUCE", "1") == "0" or not dist.is_initialized() or dist.get_backend() != "nccl":
+        _reducer_failed = True
+        return None
+    tp = dist.get_world_size()
+    if not 2 <= tp <= 8:
+        _reducer_failed = True
+        return None
+    if torch.cuda.is_current_stream_capturing():
+        return None                        # set-up allocates and talks to the peers: not during a capture
+    _reducer = P2PRowReducer(max_message_bytes(tp))
+    return _reducer

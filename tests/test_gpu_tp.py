@@ -81,6 +81,48 @@ def _worker(rank, world, port, out_path):
         # same sums up to fp32 summation order (the chunked launches may split K differently)
         err = (piped.float() - single.float()).abs().max() / single.float().abs().max()
         res["pipelined_close_to_single"] = (err <= 8e-3).to(torch.int16).reshape(1)
+        # ---- the peer-memory sum (decode-sized outputs) against NCCL's all-reduce ----
+        from nano_qwen_b200.layers import p2p_reduce
+        from nano_qwen_b200 import _cabi
+        reducer = p2p_reduce.get_reducer()
+        assert reducer is not None, "the row layers above should have created the peer-memory reducer"
+        gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+        worst = 0.0
+        for it, n in enumerate([8, 1024, 16 * 1024, 64 * 4096, 256 * 4096, 8 * 5120, 40, 64 * 4096]):
+            # back-to-back calls of changing size, nothing but the kernels' own handshake between them
+            t = torch.randn(n, generator=gen, device="cuda").to(torch.bfloat16)
+            want = t.clone()
+            dist.all_reduce(want)
+            assert reducer.fits(t), n
+            got_t = reducer.reduce_(t.clone())
+            worst = max(worst, float((got_t.float() - want.float()).abs().max() / want.float().abs().max()))
+        res["p2p_vs_nccl_ok"] = torch.tensor([1 if worst <= 2 ** -7 else 0], dtype=torch.int16)
+        # a graph that holds nothing but one row layer, replayed with fresh inputs: the call counter lives on the device
+        row = rows["o_proj"]
+        xs = torch.zeros(16, shapes["o_proj"][0] // world, dtype=torch.bfloat16, device="cuda")
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            row(xs)
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(g):
+            yg = row(xs)
+        replay_ok = 1
+        for it in range(6):
+            xs.copy_(torch.randn(xs.shape, generator=gen, device="cuda").to(torch.bfloat16))
+            g.replay()
+            row.p2p_reduce = False
+            ref = row(xs)                                   # eager GEMM + NCCL
+            row.p2p_reduce = True
+            torch.cuda.synchronize()
+            err = float((yg.float() - ref.float()).abs().max() / ref.float().abs().max())
+            replay_ok &= int(err <= 2 ** -7)
+        res["p2p_graph_replays_ok"] = torch.tensor([replay_ok], dtype=torch.int16)
+        res["p2p_result_for_rank_equality"] = yg.clone().reshape(-1)
+        del g, yg
+        torch.cuda.synchronize()
+        res["device_status"] = torch.tensor([_cabi.device_status()["code"]], dtype=torch.int16)
         np.savez(out_path.format(rank=rank), **{k: v.cpu().view(torch.int16).numpy() for k, v in res.items()})
         dist.barrier()
     except BaseException:
@@ -110,5 +152,9 @@ def test_two_gpu_layers_match_the_reference_two_rank_run(tmp_path, built_library
             for name in ("o_proj", "down"):
                 assert np.array_equal(got[r][name], got[r][name + "_graph"]), name     # graph replay == eager
             assert int(got[r]["pipelined_close_to_single"][0]) == 1
+            assert int(got[r]["p2p_vs_nccl_ok"][0]) == 1
+            assert int(got[r]["p2p_graph_replays_ok"][0]) == 1
+            assert int(got[r]["device_status"][0]) == 0
+        assert np.array_equal(got[0]["p2p_result_for_rank_equality"], got[1]["p2p_result_for_rank_equality"])
         for name in ("o_proj", "down"):
             assert np.array_equal(got[0][name], got[1][name])                          # both ranks hold the sum
