@@ -152,19 +152,18 @@ int nq_fp8_linear_noalloc(const void* x, int64_t ldx,
 
 /* ---- Row-parallel reduction over peer memory (one process per GPU, all GPUs of one node) ------------------
  * Stands in for the `dist.all_reduce(y)` that ends RowParallelLinear.forward (linear.py:154-155) when y is
- * small (decode batches): one kernel per rank pushes its partial into every peer's inbox over NVLink, waits
- * (bounded) for the peers' partials and adds them in rank order in fp32, so every rank ends with the same
- * bf16 bits.  Legal inside CUDA-graph capture: the call number lives in device memory.
+ * small (decode batches): one kernel per rank pushes its partial into every peer's inbox over NVLink (each
+ * 8-byte word carries 4 bytes of data and the call number, so no fence and no second trip are needed), polls
+ * (bounded) its own inbox for the peers' partials and adds them in rank order in fp32, so every rank ends
+ * with the same bf16 bits.  Legal inside CUDA-graph capture: the call number lives in device memory.
  *
  * Set-up, once per process (host side; the caller moves the 64-byte handles between processes itself):
- *   inbox : nq_p2p_alloc(2 * tp * slot_bytes)             zero-filled device memory of the current device
- *   flags : nq_p2p_alloc(tp * NQ_P2P_MAX_BLOCKS * 4)
- *   state : nq_p2p_alloc(256)                              private to the rank, never exported
- *   nq_p2p_export(ptr, handle) on the owner, nq_p2p_import(handle, &ptr) on every peer, then a barrier
+ *   inbox : nq_p2p_alloc(4 * tp * slot_bytes)    zero-filled device memory of the current device
+ *   state : nq_p2p_alloc(256)                     private to the rank, never exported
+ *   nq_p2p_export(inbox, handle) on the owner, nq_p2p_import(handle, &ptr) on every peer, then a barrier
  *   between the processes before the first reduction.
  * All ranks must make the same sequence of nq_row_reduce_p2p calls (same count, same slot_bytes). */
 #define NQ_P2P_MAX_RANKS 8
-#define NQ_P2P_MAX_BLOCKS 512
 #define NQ_P2P_HANDLE_BYTES 64
 int nq_p2p_alloc(size_t bytes, void** dev_ptr);
 int nq_p2p_free(void* dev_ptr);                                   /* memory from nq_p2p_alloc */
@@ -173,12 +172,12 @@ int nq_p2p_import(const unsigned char* handle, void** dev_ptr);   /* maps a peer
 int nq_p2p_release(void* dev_ptr);                                /* unmaps a pointer from nq_p2p_import */
 
 /* y[i] = bf16( sum over ranks r = 0..tp-1 of partial_r[i] ), i < count (bf16 elements; count % 8 == 0,
- * count * 2 <= slot_bytes, both pointers 16-byte aligned; y may be the same buffer as partial).
- * inbox / flags: HOST arrays of tp device pointers, entry r = rank r's inbox / flag array as mapped in this
- * process (entry `rank` is the local allocation).  A peer that never arrives makes the bounded wait expire:
- * the call still completes and nq_device_status reports NQ_ERR_DEVICE_TIMEOUT. */
+ * count * 2 <= slot_bytes, slot_bytes % 16 == 0, both pointers 16-byte aligned; y may be the same buffer as
+ * partial).  inbox: HOST array of tp device pointers, entry r = rank r's inbox as mapped in this process
+ * (entry `rank` is the local allocation).  A peer that never arrives makes the bounded wait expire: the call
+ * still completes and nq_device_status reports NQ_ERR_DEVICE_TIMEOUT. */
 int nq_row_reduce_p2p(const void* partial, void* y, int64_t count,
-                      void* const* inbox, void* const* flags, int rank, int tp,
+                      void* const* inbox, int rank, int tp,
                       int64_t slot_bytes, void* state, void* stream);
 
 /* Reads the device-side status block of the current device (mapped host

@@ -41,7 +41,7 @@ SIGNATURES = {
     "nq_p2p_export": (c_int, [c_void_p, c_void_p]),
     "nq_p2p_import": (c_int, [c_void_p, POINTER(c_void_p)]),
     "nq_p2p_release": (c_int, [c_void_p]),
-    "nq_row_reduce_p2p": (c_int, [c_void_p, c_void_p, c_int64, POINTER(c_void_p), POINTER(c_void_p), c_int, c_int,
+    "nq_row_reduce_p2p": (c_int, [c_void_p, c_void_p, c_int64, POINTER(c_void_p), c_int, c_int,
                                   c_int64, c_void_p, c_void_p]),
     "nq_device_status": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]),
     "nq_set_wait_limit_ns": (c_int, [c_uint64]),

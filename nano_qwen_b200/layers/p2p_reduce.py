@@ -2,8 +2,8 @@
 
 Stands in for the ``dist.all_reduce(y)`` that ends the reference's ``RowParallelLinear.forward``
 (``nano_qwen/layers/linear.py:154-155``) when ``y`` is small: NCCL's all-reduce costs a fixed latency per call that
-dominates a 16-512 KiB message, one kernel that pushes the partial to every peer over NVLink and adds what the peers
-pushed does not.  Larger messages keep NCCL (a one-shot exchange moves ``tp - 1`` copies of the message per GPU).
+dominates a 16-512 KiB message, one kernel that pushes the partial to every peer over NVLink (data and call number in the same 8-byte words) and
+adds what the peers pushed does not.  Larger messages keep NCCL (a one-shot exchange moves ``tp - 1`` copies of the message per GPU).
 
 ``torch.distributed`` is only the plumbing: it carries the 64-byte IPC handles between the ranks at set-up.
 All ranks must be processes on one node, one GPU each.
@@ -18,12 +18,11 @@ import torch.distributed as dist
 
 from .. import _cabi
 
-_P2P_MAX_BLOCKS = 512          # NQ_P2P_MAX_BLOCKS
 _HANDLE_BYTES = 64             # NQ_P2P_HANDLE_BYTES
 
 
 class P2PRowReducer:
-    """One per process: inbox, flags and call counter of this rank plus the mapped inboxes / flags of the peers."""
+    """One per process: inbox and call counter of this rank plus the mapped inboxes of the peers."""
 
     def __init__(self, slot_bytes: int, group=None):
         self.group = group
@@ -35,23 +34,23 @@ class P2PRowReducer:
         lib = _cabi.lib()
         self._own = []
         mine = {}
-        for name, size in (("inbox", 2 * self.tp * self.slot_bytes), ("flags", self.tp * _P2P_MAX_BLOCKS * 4),
-                           ("state", 256)):
+        # a slot holds the message twice over: every 8-byte word is 4 bytes of data + the call number
+        for name, size in (("inbox", 2 * self.tp * 2 * self.slot_bytes), ("state", 256)):
             ptr = ctypes.c_void_p()
             _cabi.check(lib.nq_p2p_alloc(size, ctypes.byref(ptr)), "nq_p2p_alloc")
             mine[name] = ptr.value
             self._own.append(ptr.value)
         handles = {}
-        for name in ("inbox", "flags"):
+        for name in ("inbox",):
             buf = (ctypes.c_ubyte * _HANDLE_BYTES)()
             _cabi.check(lib.nq_p2p_export(mine[name], buf), "nq_p2p_export")
             handles[name] = bytes(buf)
         gathered = [None] * self.tp
         dist.all_gather_object(gathered, handles, group=group)
         self._mapped = []
-        ptrs = {"inbox": [], "flags": []}
+        ptrs = {"inbox": []}
         for r in range(self.tp):
-            for name in ("inbox", "flags"):
+            for name in ("inbox",):
                 if r == self.rank:
                     ptrs[name].append(mine[name])
                     continue
@@ -61,9 +60,8 @@ class P2PRowReducer:
                 ptrs[name].append(ptr.value)
                 self._mapped.append(ptr.value)
         self._inbox = (ctypes.c_void_p * self.tp)(*ptrs["inbox"])
-        self._flags = (ctypes.c_void_p * self.tp)(*ptrs["flags"])
         self._state = mine["state"]
-        dist.barrier(group=group)          # every inbox and flag array exists and is zero before anyone pushes
+        dist.barrier(group=group)          # every inbox exists and is zero before anyone pushes
 
     def fits(self, y: torch.Tensor) -> bool:
         n = y.numel()
@@ -72,7 +70,7 @@ class P2PRowReducer:
 
     def reduce_(self, y: torch.Tensor) -> torch.Tensor:
         """In-place SUM of ``y`` over the ranks; enqueued on the current stream (capturable)."""
-        st = _cabi.lib().nq_row_reduce_p2p(y.data_ptr(), y.data_ptr(), y.numel(), self._inbox, self._flags, self.rank,
+        st = _cabi.lib().nq_row_reduce_p2p(y.data_ptr(), y.data_ptr(), y.numel(), self._inbox, self.rank,
                                            self.tp, self.slot_bytes, self._state,
                                            torch.cuda.current_stream().cuda_stream)
         _cabi.check(st, "nq_row_reduce_p2p")
