@@ -94,6 +94,28 @@ int nq_act_quant_e4m3_g128(const void* x, int64_t M, int64_t K, int64_t ldx,
 int nq_weight_quant_e4m3_b128(const void* w, int64_t N, int64_t K, int64_t ldw,
                               void* wq, int64_t ld_wq, float* sw, int64_t ld_sw, void* stream);
 
+/* ---- Producers that emit FP8 directly (the quantiser fused into the op in front of a linear layer) --------
+ * Same output contract as nq_act_quant_e4m3_g128 (xq / sx layouts, scale rule); the value that is quantised is
+ * the bf16 tensor the reference's eager code would have produced.  Vector path only: the feature size must be
+ * a multiple of 16, row strides multiples of 8 elements (16 bytes for xq), pointers 16-byte aligned; anything
+ * else returns NQ_ERR_UNSUPPORTED (run the reference op and nq_act_quant_e4m3_g128 instead).
+ *
+ * nq_silu_mul_quant_e4m3_g128: gate_up [M, 2*I] bf16 (gate = columns [0, I), up = [I, 2I)), row stride `ld`;
+ *   h = bf16(bf16(silu(gate)) * up), silu evaluated in fp32 — SiluAndMul.forward, layers/activation.py:8-11;
+ *   xq [M, I], sx [ceil(I/128), ld_sx]: the input of down_proj. */
+int nq_silu_mul_quant_e4m3_g128(const void* gate_up, int64_t M, int64_t I, int64_t ld,
+                                void* xq, int64_t ld_xq, float* sx, int64_t ld_sx, void* stream);
+
+/* nq_rmsnorm_quant_e4m3_g128: RMSNorm.forward / GemmaRMSNorm.forward (layers/layernorm.py:16-56, :79-120).
+ *   v = float(x) [+ float(residual_in)];  residual_out = bf16(v) (only with residual_in; may be the same buffer);
+ *   n = bf16(v * rsqrt(mean(v^2) + eps));  h = bf16(n * weight)  or, gemma != 0,  bf16(n * bf16(1 + weight));
+ *   xq / sx = quantised h; y_out (optional, may be NULL) receives h in bf16 for consumers that are not FP8 linears.
+ *   weight [H] bf16; x, residual, y_out [M, H] bf16 with row strides ldx, ld_res, ldy. */
+int nq_rmsnorm_quant_e4m3_g128(const void* x, const void* residual_in, const void* weight, float eps, int gemma,
+                               int64_t M, int64_t H, int64_t ldx, int64_t ld_res, void* residual_out,
+                               void* y_out, int64_t ldy,
+                               void* xq, int64_t ld_xq, float* sx, int64_t ld_sx, void* stream);
+
 /* Bytes of zero-initialised scratch the GEMM may need for this problem.
  * The buffer must be zero-filled ONCE by the caller before its first use; the
  * library leaves it in a reusable state after every launch.  Two launches that

@@ -26,6 +26,10 @@ SIGNATURES = {
     "nq_init": (c_int, []),
     "nq_act_quant_e4m3_g128": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "nq_weight_quant_e4m3_b128": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "nq_silu_mul_quant_e4m3_g128": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "nq_rmsnorm_quant_e4m3_g128": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_float, c_int, c_int64, c_int64, c_int64,
+                                           c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                           c_void_p]),
     "nq_fp8_gemm_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "nq_fp8_gemm_bs128": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                   c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,

@@ -976,19 +976,12 @@ __device__ __noinline__ uint2 quantise8_e4m3_ieee(uint4 raw, float scale) {
 template <int NR>
 __device__ __forceinline__ void quantise_rows_e4m3(const uint4 (&raw)[NR], uint32_t mask16, uint2 (&q)[NR],
                                                    float (&scale)[NR]) {
-  float v[NR][8], y[NR];
+  float y[NR];
   bool slow = false;
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
-    const uint32_t w4[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      v[r][2 * e] = bf16_bits_to_float(w4[e] & 0xFFFFu);
-      v[r][2 * e + 1] = bf16_bits_to_float(w4[e] >> 16);
-    }
-    float amax = 0.0f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[r][e]));
+    const uint32_t m2 = bf16x2_absmax(bf16x2_absmax(raw[r].x, raw[r].y), bf16x2_absmax(raw[r].z, raw[r].w));
+    float amax = fmaxf(bf16_bits_to_float(m2 & 0xFFFFu), bf16_bits_to_float(m2 >> 16));
     amax = fmaxf(amax, __shfl_xor_sync(mask16, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(mask16, amax, 2));
     amax = fmaxf(amax, __shfl_xor_sync(mask16, amax, 4));
@@ -1005,13 +998,14 @@ __device__ __forceinline__ void quantise_rows_e4m3(const uint4 (&raw)[NR], uint3
   }
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
+    ExactDivider div(scale[r]);
+    div.y = y[r];
+    const uint32_t w[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
+    float2 v[4];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float q0 = __fmul_rn(v[r][e], y[r]);
-      const float rem = __fmaf_rn(-scale[r], q0, v[r][e]);
-      v[r][e] = __fmaf_rn(rem, y[r], q0);
-    }
-    q[r] = make_uint2(pack4_e4m3(v[r][0], v[r][1], v[r][2], v[r][3]), pack4_e4m3(v[r][4], v[r][5], v[r][6], v[r][7]));
+    for (int e = 0; e < 4; ++e)
+      v[e] = div.fast2(make_float2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xFFFF0000u)));
+    q[r] = make_uint2(pack4_e4m3(v[0].x, v[0].y, v[1].x, v[1].y), pack4_e4m3(v[2].x, v[2].y, v[3].x, v[3].y));
   }
 }
 

@@ -407,7 +407,22 @@ struct ExactDivider {
     const float r = __fmaf_rn(-s, q0, x);
     return __fmaf_rn(r, y, q0);
   }
+  // Two quotients with packed two-wide instructions (same IEEE operations per lane); only for !slow.
+  __device__ __forceinline__ float2 fast2(float2 x) const {
+    const float2 y2 = make_float2(y, y);
+    const float2 q0 = __fmul2_rn(x, y2);
+    const float2 r = __ffma2_rn(make_float2(-s, -s), q0, x);
+    return __ffma2_rn(r, y2, q0);
+  }
 };
+
+// |a| max |b| element-wise on packed bf16 pairs (exact: a maximum never rounds).
+__device__ __forceinline__ uint32_t bf16x2_absmax(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 x = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&a));
+  const __nv_bfloat162 y = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&b));
+  const __nv_bfloat162 m = __hmax2(x, y);
+  return *reinterpret_cast<const uint32_t*>(&m);
+}
 
 __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
   const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);

@@ -26,30 +26,45 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __nv_bfloat16* __r
   const int64_t items = M * G;
   const int sub = threadIdx.x >> 3;   // 0..31 sub-warp within the block
   const int l8 = threadIdx.x & 7;     // lane within the sub-warp
-  for (int64_t item = static_cast<int64_t>(blockIdx.x) * 32 + sub; item < items;
-       item += static_cast<int64_t>(gridDim.x) * 32) {
+  // Grid-stride loop; the aligned variant requests the next item's 32 bytes before it converts the current one.
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 32;
+  int64_t item = static_cast<int64_t>(blockIdx.x) * 32 + sub;
+  uint4 na = make_uint4(0u, 0u, 0u, 0u), nb = na;
+  if (VEC && item < items) {
+    const int64_t m = item / G, g = item - m * G;
+    const uint4* src = reinterpret_cast<const uint4*>(x + m * ldx + (g << 7) + (l8 << 4));
+    na = __ldg(src);
+    nb = __ldg(src + 1);
+  }
+  for (; item < items; item += stride) {
     const int64_t m = item / G;
     const int64_t g = item - m * G;
     const int64_t k0 = (g << 7) + (l8 << 4);
-    float v[16];
+    // the 16 elements as 8 words of two bf16 each (element 2i in the low half of word i)
+    uint32_t w[8];
     if (VEC) {
-      const uint4* src = reinterpret_cast<const uint4*>(x + m * ldx + k0);
-      const uint4 a = __ldg(src);
-      const uint4 b = __ldg(src + 1);
-      const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        v[2 * i] = bf16_bits_to_float(w[i] & 0xFFFFu);
-        v[2 * i + 1] = bf16_bits_to_float(w[i] >> 16);
+      w[0] = na.x; w[1] = na.y; w[2] = na.z; w[3] = na.w; w[4] = nb.x; w[5] = nb.y; w[6] = nb.z; w[7] = nb.w;
+      const int64_t nxt = item + stride;
+      if (nxt < items) {
+        const int64_t m1 = nxt / G, g1 = nxt - m1 * G;
+        const uint4* src = reinterpret_cast<const uint4*>(x + m1 * ldx + (g1 << 7) + (l8 << 4));
+        na = __ldg(src);
+        nb = __ldg(src + 1);
       }
     } else {
       const unsigned short* src = reinterpret_cast<const unsigned short*>(x + m * ldx);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = (k0 + i < K) ? bf16_bits_to_float(src[k0 + i]) : 0.0f;
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t lo = (k0 + 2 * i < K) ? src[k0 + 2 * i] : 0u;
+        const uint32_t hi = (k0 + 2 * i + 1 < K) ? src[k0 + 2 * i + 1] : 0u;
+        w[i] = lo | (hi << 16);
+      }
     }
-    float amax = 0.0f;
+    // amax on the packed pairs (a maximum of bf16 values is exact), then across the pair and the sub-warp
+    uint32_t m2 = bf16x2_absmax(w[0], w[1]);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    for (int i = 2; i < 8; i += 2) m2 = bf16x2_absmax(m2, bf16x2_absmax(w[i], w[i + 1]));
+    float amax = fmaxf(bf16_bits_to_float(m2 & 0xFFFFu), bf16_bits_to_float(m2 >> 16));
     // sub-warps of one warp may leave the loop at different items: mask = own 8 lanes
     const uint32_t mask8 = 0xFFu << (threadIdx.x & 24);
     amax = fmaxf(amax, __shfl_xor_sync(mask8, amax, 1));
@@ -58,20 +73,28 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __nv_bfloat16* __r
     const float scale = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
     if (l8 == 0) sx[g * ld_sx + m] = scale;
     const ExactDivider div(scale);
+    uint32_t qw[4];
+    if (!div.slow) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = div(v[i]);
-    uint4 q;
-    q.x = pack4_e4m3(v[0], v[1], v[2], v[3]);
-    q.y = pack4_e4m3(v[4], v[5], v[6], v[7]);
-    q.z = pack4_e4m3(v[8], v[9], v[10], v[11]);
-    q.w = pack4_e4m3(v[12], v[13], v[14], v[15]);
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = div.fast2(make_float2(__uint_as_float(w[2 * i] << 16), __uint_as_float(w[2 * i] & 0xFFFF0000u)));
+        const float2 b = div.fast2(make_float2(__uint_as_float(w[2 * i + 1] << 16), __uint_as_float(w[2 * i + 1] & 0xFFFF0000u)));
+        qw[i] = pack4_e4m3(a.x, a.y, b.x, b.y);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        qw[i] = pack4_e4m3(__fdiv_rn(__uint_as_float(w[2 * i] << 16), scale), __fdiv_rn(__uint_as_float(w[2 * i] & 0xFFFF0000u), scale),
+                           __fdiv_rn(__uint_as_float(w[2 * i + 1] << 16), scale), __fdiv_rn(__uint_as_float(w[2 * i + 1] & 0xFFFF0000u), scale));
+      }
+    }
+    const uint4 q = make_uint4(qw[0], qw[1], qw[2], qw[3]);
     if (VEC) {
       *reinterpret_cast<uint4*>(xq + m * ld_xq + k0) = q;
     } else {
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
       for (int i = 0; i < 16; ++i)
-        if (k0 + i < K) xq[m * ld_xq + k0 + i] = static_cast<uint8_t>(w[i >> 2] >> ((i & 3) * 8));
+        if (k0 + i < K) xq[m * ld_xq + k0 + i] = static_cast<uint8_t>(qw[i >> 2] >> ((i & 3) * 8));
     }
   }
   pdl_launch_next();
@@ -159,7 +182,11 @@ int launch_act_quant(const void* x, int64_t M, int64_t K, int64_t ldx, void* xq,
   const bool vec = (K % 128 == 0) && (ldx % 8 == 0) && (ld_xq % 16 == 0) &&
                    (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(xq) % 16 == 0);
   int64_t blocks = (items + 31) / 32;
-  const int64_t cap = 148 * 64;
+  DeviceCtx* ctx = nullptr;
+  const int st = ensure_init(&ctx);
+  if (st != NQ_OK) return st;
+  // grid-stride loop over at most 32 CTAs per SM (several waves smooth the tail; measured equal from 10 to 64)
+  const int64_t cap = static_cast<int64_t>(ctx->sm_count) * 32;
   if (blocks > cap) blocks = cap;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(blocks));

@@ -1,3 +1,6 @@
+from .activation import SiluAndMul
+from .layernorm import GemmaRMSNorm, RMSNorm
+from .quantized import QuantizedActivation
 from .linear import (
     ColumnParallelLinear,
     LinearBase,
@@ -16,4 +19,8 @@ __all__ = [
     "QKVParallelLinear",
     "RowParallelLinear",
     "divide",
+    "SiluAndMul",
+    "RMSNorm",
+    "GemmaRMSNorm",
+    "QuantizedActivation",
 ]

@@ -25,12 +25,15 @@ matching rows of ``weight_scale_inv``.  Shard boundaries must fall on
 """
 from __future__ import annotations
 
+import math
+
 import torch
 import torch.distributed as dist
 from torch import nn
 
 from .. import ops
 from . import p2p_reduce
+from .quantized import QuantizedActivation
 
 BLOCK = 128
 FP8 = torch.float8_e4m3fn
@@ -114,7 +117,10 @@ class LinearBase(nn.Module):
         off, size = self._to_units(self.weight_scale_inv, dim, dst_offset, dst_size)
         self.weight_scale_inv.data.narrow(dim, off, size).copy_(sw)
 
-    def _linear(self, x: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+    def _linear(self, x, bias: torch.Tensor | None) -> torch.Tensor:
+        if isinstance(x, QuantizedActivation):       # a fused producer already quantised it: GEMM only
+            y = ops.fp8_gemm(x.xq, x.sx, self.weight, self.weight_scale_inv, bias)
+            return y.view(*x.shape[:-1], y.shape[-1])
         return ops.fp8_linear(x, self.weight, self.weight_scale_inv, bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -232,8 +238,8 @@ class RowParallelLinear(LinearBase):
         bias = self.bias if self.tp_rank == 0 else None          # added once, before the sum
         if self.tp_size == 1:
             return self._linear(x, bias)
-        rows = x.numel() // max(x.shape[-1], 1)
-        chunks = min(self.overlap_chunks, rows // self.overlap_min_rows)
+        rows = math.prod(x.shape[:-1])
+        chunks = 0 if isinstance(x, QuantizedActivation) else min(self.overlap_chunks, rows // self.overlap_min_rows)
         if chunks < 2 or not x.is_cuda or torch.cuda.is_current_stream_capturing():
             y = self._linear(x, bias)
             reducer = p2p_reduce.get_reducer() if (self.p2p_reduce and x.is_cuda) else None

@@ -75,6 +75,70 @@ def act_quant(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return xq_buf[:, :K], sx_buf[:, :M].t()
 
 
+def _quant_buffers(M: int, K: int, device) -> tuple[torch.Tensor, torch.Tensor, int, int]:
+    G = (K + GROUP - 1) // GROUP
+    ld_xq = _round_up(max(K, 1), 16)
+    ld_sx = _round_up(max(M, 1), 4)
+    return (torch.empty((M, ld_xq), dtype=FP8, device=device), torch.empty((G, ld_sx), dtype=torch.float32, device=device),
+            ld_xq, ld_sx)
+
+
+def silu_mul_quant(gate_up: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``silu(gate) * up`` of a ``[M, 2*I]`` bf16 tensor (gate first), emitted as FP8 + 1x128 group scales.
+
+    Stands in for the reference's ``SiluAndMul.forward`` (``layers/activation.py:8-11``) followed by the activation
+    quantiser of the next linear layer.  Returns ``(xq, sx)`` laid out like :func:`act_quant`'s.
+    """
+    _require_cuda(gate_up)
+    if gate_up.dtype != torch.bfloat16 or gate_up.dim() != 2 or gate_up.shape[1] % 2:
+        raise TypeError("silu_mul_quant expects a 2-D bfloat16 tensor with an even number of columns")
+    if gate_up.stride(1) != 1:
+        gate_up = gate_up.contiguous()
+    M, I = gate_up.shape[0], gate_up.shape[1] // 2
+    xq_buf, sx_buf, ld_xq, ld_sx = _quant_buffers(M, I, gate_up.device)
+    if M > 0 and I > 0:
+        st = _cabi.lib().nq_silu_mul_quant_e4m3_g128(gate_up.data_ptr(), M, I, gate_up.stride(0) if M > 1 else 2 * I,
+                                                     xq_buf.data_ptr(), ld_xq, sx_buf.data_ptr(), ld_sx, _stream())
+        _cabi.check(st, "nq_silu_mul_quant_e4m3_g128")
+    return xq_buf[:, :I], sx_buf[:, :M].t()
+
+
+def rmsnorm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None,
+                  gemma: bool = False, want_bf16: bool = False):
+    """RMS norm of ``[M, H]`` bf16 rows (optionally after adding ``residual``), emitted as FP8 + group scales.
+
+    Stands in for ``RMSNorm.forward`` / ``GemmaRMSNorm.forward`` (``layers/layernorm.py:16-56``, ``:79-120``) followed
+    by the activation quantiser.  Returns ``(xq, sx, new_residual_or_None, bf16_result_or_None)``.
+    """
+    _require_cuda(x, weight, residual)
+    if x.dtype != torch.bfloat16 or x.dim() != 2:
+        raise TypeError("rmsnorm_quant expects a 2-D bfloat16 tensor")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    M, H = x.shape
+    if weight.dtype != torch.bfloat16 or weight.numel() != H:
+        weight = weight.to(torch.bfloat16)
+    weight = weight.contiguous()
+    res_out = None
+    if residual is not None:
+        if residual.dtype != torch.bfloat16 or residual.shape != x.shape:
+            raise TypeError("residual must be bfloat16 with the shape of x")
+        if residual.stride(1) != 1:
+            residual = residual.contiguous()
+        res_out = torch.empty((M, H), dtype=torch.bfloat16, device=x.device)
+    y = torch.empty((M, H), dtype=torch.bfloat16, device=x.device) if want_bf16 else None
+    xq_buf, sx_buf, ld_xq, ld_sx = _quant_buffers(M, H, x.device)
+    if M > 0 and H > 0:
+        st = _cabi.lib().nq_rmsnorm_quant_e4m3_g128(
+            x.data_ptr(), residual.data_ptr() if residual is not None else None, weight.data_ptr(), float(eps),
+            int(bool(gemma)), M, H, x.stride(0) if M > 1 else H,
+            (residual.stride(0) if M > 1 else H) if residual is not None else 0,
+            res_out.data_ptr() if res_out is not None else None, y.data_ptr() if y is not None else None, H,
+            xq_buf.data_ptr(), ld_xq, sx_buf.data_ptr(), ld_sx, _stream())
+        _cabi.check(st, "nq_rmsnorm_quant_e4m3_g128")
+    return xq_buf[:, :H], sx_buf[:, :M].t(), res_out, y
+
+
 def weight_quant(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """Offline 128x128 block quantiser: bf16 ``[N, K]`` -> (e4m3 ``[N, K]``, fp32 ``[ceil(N/128), ceil(K/128)]``)."""
     _require_cuda(w)

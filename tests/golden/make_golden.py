@@ -19,6 +19,10 @@ What it records
     through their loaders and run through their ``forward`` on CPU in fp32
     (row-parallel layers all-reduced over gloo).  Outputs are stored as bf16
     bit patterns, inputs as sha256 digests.
+``fused_ops.npz``
+    The reference's ``SiluAndMul``, ``RMSNorm`` and ``GemmaRMSNorm`` (``layers/activation.py``, ``layers/layernorm.py``)
+    run on CPU in bf16 with ``torch.compile`` switched off (``TORCHDYNAMO_DISABLE=1``), on seeded inputs of the
+    Qwen3-0.6B shapes at M=16: inputs and outputs as bf16 bit patterns.
 """
 from __future__ import annotations
 
@@ -167,10 +171,43 @@ def worker(rank: int, tp: int, port: int, ref_src: str, outdir: str):
     dist.destroy_process_group()
 
 
+def fused_ops(ref_src: str) -> None:
+    """Runs in a child interpreter: the compiler switch has to be set before torch is imported."""
+    import subprocess
+    code = r'''
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+from nano_qwen.layers.activation import SiluAndMul
+from nano_qwen.layers.layernorm import RMSNorm, GemmaRMSNorm
+g = torch.Generator().manual_seed(2024)
+bits = lambda t: t.contiguous().view(torch.int16).numpy()
+M, H, I = 16, 1024, 3072
+out = {}
+gate_up = (torch.randn(M, 2 * I, generator=g) * 1.5).to(torch.bfloat16)
+out["silu_in"] = bits(gate_up)
+out["silu_out"] = bits(SiluAndMul()(gate_up))
+x = torch.randn(M, H, generator=g).to(torch.bfloat16)
+res = torch.randn(M, H, generator=g).to(torch.bfloat16)
+out["norm_x"], out["norm_res"] = bits(x), bits(res)
+for name, cls in (("rms", RMSNorm), ("gemma", GemmaRMSNorm)):
+    mod = cls(H, eps=1e-6).to(torch.bfloat16)
+    w = (torch.randn(H, generator=g) * 0.3 + (0.0 if name == "gemma" else 1.0)).to(torch.bfloat16)
+    mod.weight.data.copy_(w)
+    out[name + "_w"] = bits(w)
+    out[name + "_out"] = bits(mod(x.clone()).detach())
+    y, r = mod(x.clone(), res.clone())
+    out[name + "_add_out"], out[name + "_add_res"] = bits(y.detach()), bits(r.detach())
+np.savez_compressed(sys.argv[2], **out)
+'''
+    env = dict(os.environ, TORCHDYNAMO_DISABLE="1")
+    subprocess.run([sys.executable, "-c", code, ref_src, os.path.join(HERE, "fused_ops.npz")], check=True, env=env)
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     ref_src = os.path.join(ref_root, "src")
     assert os.path.isdir(ref_src), ref_src
+    fused_ops(ref_src)
     tmp = tempfile.mkdtemp()
     sharding = {"cases": SHARD_CASES}
     for i, tp in enumerate((1, 2, 4, 8)):
