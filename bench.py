@@ -413,6 +413,47 @@ def run_gpu_arm(args) -> None:
             del xs
         del big
         torch.cuda.synchronize()
+        # ---- the producers that emit FP8 directly (the rows next to the path): HBM-bound streaming kernels.
+        #      Algorithmic bytes: silu-mul 4*M*I in + M*I + 4*M*I/128 out; add+norm 4*M*H in + 2*M*H (residual)
+        #      + M*H + 4*M*H/128 out.  Three input copies are cycled; M = 8192 eager, M = 64 from a CUDA graph ----
+        detail["producers"] = {}
+        for m in (64, 8192):
+            gu = [torch.randn((m, 2 * INTER // tp), generator=gen_d, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+                  for _ in range(3)]
+            xr = [torch.randn((m, HIDDEN), generator=gen_d, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+                  for _ in range(3)]
+            wn = torch.ones(HIDDEN, dtype=torch.bfloat16, device="cuda")
+
+            def run_silu():
+                for t in gu:
+                    ops.silu_mul_quant(t)
+
+            def run_norm():
+                for t in xr:
+                    ops.rmsnorm_quant(t, wn, 1e-6, xr[0])
+            res = {}
+            for name, fn, nbytes in (("silu_mul_quant", run_silu, m * (INTER // tp) * (4 + 1 + 4 / 128)),
+                                     ("add_rmsnorm_quant", run_norm, m * HIDDEN * (4 + 2 + 1 + 4 / 128))):
+                if m <= 64:
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side):
+                        fn()
+                    torch.cuda.current_stream().wait_stream(side)
+                    torch.cuda.synchronize()
+                    gm = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gm):
+                        for _ in range(8):
+                            fn()
+                    ms, _ = timed(gm.replay, 5, 2)
+                    us = ms * 1e3 / 24
+                    del gm
+                else:
+                    ms, _ = timed(fn, 5, 2)
+                    us = ms * 1e3 / 3
+                res[name] = {"us": round(us, 2), "hbm_gbs": round(nbytes / (us * 1e-6) / 1e9, 1)}
+            detail["producers"][str(m)] = res
+            del gu, xr
+        torch.cuda.synchronize()
     status = _cabi.device_status()
 
     if rank == 0:
