@@ -121,8 +121,13 @@ struct TokenLane {
   static constexpr int kGroupM = 16;                // M-tiles per rasterisation group
   static constexpr int kScalePrefetch = 4;          // K-tiles of scale factors in flight in the loader warp
   // register split between the first warpgroup and the epilogue warpgroups (setmaxnreg)
-  static constexpr int kRegsLow = 56;
-  static constexpr int kRegsHigh = (kThreads == 512) ? 152 : 224;
+  // (a warpgroup that asks for more registers than the CTA's pool holds would wait for ever: the sum over the
+  //  warpgroups must not exceed what the kernel is launched with - checked here against the launch-bounds figure
+  //  and again on the host, against the compiled kernel, before the first launch)
+  static constexpr int kRegsLow = (kThreads == 512) ? 56 : 64;
+  static constexpr int kRegsHigh = (kThreads == 512) ? 152 : 216;
+  static constexpr int kRegsNeeded = kRegsLow + (kThreads / 128 - 1) * kRegsHigh;
+  static_assert(kRegsNeeded <= (65536 / kThreads / 8 * 8) * (kThreads / 128), "setmaxnreg split exceeds the register pool");
 };
 
 struct TokenLaneParams {
@@ -135,7 +140,6 @@ struct TokenLaneParams {
   int y_vec;                  // 1: 16-byte stores are legal for y
   int y_tma;                  // 1: the output tensor map is valid (y 16-byte aligned, row stride a multiple of 16 bytes)
   int sx_vec;                 // 1: 16-byte loads of sx rows are legal
-  int debug;                  // experiments only (0 in normal operation)
   long long* prof;            // cycle accounting buffer (profiling builds) or null
   uint32_t wait_mode;         // 0 try_wait, 1 test_wait spin, >1 try_wait with that suspend hint (ns)
   DeviceStatus* status;
@@ -271,16 +275,15 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     // commits); with a single issuer the tensor pipe sat idle for that time after every K-tile.  With two,
     // one thread's waits overlap the other's UMMAs.  Consecutive K-tiles use different accumulators and
     // different stages, so the two instruction streams are independent.
-    if (lane == 0 && (p.debug != 8 || warp == 1)) {
+    if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(128, BN);
       const uint32_t mine = (warp == 1) ? 0u : 1u;
-      const bool both = (p.debug != 8);            // experiments: debug 8 = single issuer
       uint32_t it = 0;
       bool ok = true;
       NQ_PROF_DECL
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         for (int kt = kt0; kt < kt1; ++kt, ++it) {
-          if (both && (it & 1u) != mine) continue;
+          if ((it & 1u) != mine) continue;
           const int b = it % C::kNumAcc;
           const uint32_t aph = (it / C::kNumAcc) & 1;
           NQ_PROF_ADD(2)
@@ -290,7 +293,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
           const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
           const uint32_t d = tmem_base + b * C::kAccStride;
-          if (p.debug != 3 && !mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
+          if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
           NQ_PROF_ADD(0)
           NQ_TRACE(0, it)
           if (!mbar_wait(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
@@ -320,7 +323,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     //   ring[b][h][row] = sx[kt, m0+row] * sw[block of column half h, kt]
     // The ring slot is the accumulator slot; this warp is the second arrival on the
     // accumulator's "full" barrier.
-    if (p.debug != 3) {
+    {
       const int nblk = (p.N + 127) >> 7;
       auto place = [&](ScaleCursor& c) {
         int m_t, n_t;
@@ -404,7 +407,6 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
       for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
       for (int kt = kt0; kt < kt1; ++kt, ++it) {
-        if (p.debug == 3) continue;   // experiments: free-running MMA, no handoff at all
         const int b = it % C::kNumAcc;
         const uint32_t aph = (it / C::kNumAcc) & 1;
         NQ_PROF_ADD(2)
@@ -415,13 +417,6 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         const float s = scale_ring[(b * C::kEpiGroups + h) * 128 + row];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * C::kAccStride + h * C::kCols;
         uint32_t ra[32], rb[32];
-        if (p.debug == 1) {           // experiments: handoff only
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
-          acc[0] += s;
-          continue;
-        }
         // Two TMEM loads in flight; the accumulator is handed back as soon as the
         // last load has landed, the remaining FMAs run while the next UMMAs execute.
         tmem_ld_32x32(taddr, ra);
@@ -606,6 +601,10 @@ struct TokenPair {
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + 1024;
   static constexpr int kGroupM = 8;                             // pair-tiles (256 rows) per rasterisation group
   static constexpr int kScalePrefetch = 4;
+  static constexpr int kRegsLow = 56;
+  static constexpr int kRegsHigh = 224;
+  static constexpr int kRegsNeeded = kRegsLow + (kThreads / 128 - 1) * kRegsHigh;
+  static_assert(kRegsNeeded <= (65536 / kThreads / 8 * 8) * (kThreads / 128), "setmaxnreg split exceeds the register pool");
 };
 
 struct __align__(8) PairBars {
@@ -675,7 +674,7 @@ token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int KT = (p.K + kTileK - 1) / kTileK;
 
   if (warp < C::kFirstEpiWarp) {
-   setmaxnreg_dec<56>();
+   setmaxnreg_dec<C::kRegsLow>();
    if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
     if (lane == 0) {
@@ -799,7 +798,7 @@ token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
    }
   } else {
-    setmaxnreg_inc<224>();
+    setmaxnreg_inc<C::kRegsHigh>();
     // ------------------------------ epilogue (both CTAs) ------------------------------
     const int q = warp & 3;
     const int h = (warp - C::kFirstEpiWarp) >> 2;
@@ -907,6 +906,8 @@ struct WeightLane {
   static constexpr int kRegsHigh = 96;
   static constexpr int kRegsQuant = 104;
   static_assert(!FUSED || TOK == 32, "the fused quantiser is built for the 32-token tile only");
+  static constexpr int kRegsNeeded = kRegsLow + kRegsHigh + kRegsQuant;    // the three warpgroups of the fused kernel
+  static_assert(!FUSED || kRegsNeeded <= (65536 / (kThreads * kMinCtas) / 8 * 8) * 3, "setmaxnreg split exceeds the register pool");
   static constexpr int kCols = TOK / (kEpiWarps / 4);     // accumulator columns per epilogue thread
   static constexpr int kNumAcc = (TOK == 256) ? 2 : 4;
   static constexpr int kTmemCols = (kNumAcc * TOK) < 32 ? 32 : (kNumAcc * TOK);
@@ -1478,13 +1479,12 @@ int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
   p.y_tma = 0;
   CUtensorMap tm_y = tm_x;                                     // placeholder when TMA stores are not possible
-  if (C::kTmaStore && p.y_vec && splits == 1 && !getenv("NQ_NO_TMA_STORE")) {
+  if (C::kTmaStore && p.y_vec && splits == 1) {
     st = make_tmap_bf16_2d(&tm_y, a.y, a.M, a.N, a.ldy, 32, 16);
     if (st != NQ_OK) return st;
     p.y_tma = 1;
   }
   p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
-  p.debug = getenv("NQ_DEBUG_EPI") ? atoi(getenv("NQ_DEBUG_EPI")) : 0;
   p.prof = g_prof_buffer;
   p.wait_mode = 0;
   p.status = ctx->status_dev;
@@ -1519,7 +1519,6 @@ int run_token_pair(const GemmArgs& a, DeviceCtx* ctx) {
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
   p.y_tma = 0;
   p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
-  p.debug = 0;
   p.prof = nullptr;
   p.wait_mode = 0;
   p.status = ctx->status_dev;
@@ -1648,6 +1647,20 @@ int setup_gemm_kernels() {
   NQ_SET_SMEM((weight_lane_kernel<256, false>), (WeightLane<256>::kSmemBytes))
   NQ_SET_SMEM((weight_lane_kernel<32, true>), (WeightLane<32, true>::kSmemBytes))
 #undef NQ_SET_SMEM
+  // Kernels whose warpgroups trade registers: the compiled kernel must be launched with at least the registers
+  // the warpgroups will ask for in total, or a setmaxnreg.inc would wait for ever.  Refuse to run instead.
+  cudaFuncAttributes fa;
+#define NQ_CHECK_REGS(kern, threads, needed)                                                      \
+  e = cudaFuncGetAttributes(&fa, kern);                                                           \
+  if (e != cudaSuccess) return check_cuda(e);                                                     \
+  if (fa.numRegs * ((threads) / 128) < (needed)) return NQ_ERR_UNSUPPORTED;
+  NQ_CHECK_REGS(token_pair_kernel<128>, TokenPair<128>::kThreads, TokenPair<128>::kRegsNeeded)
+  NQ_CHECK_REGS(token_pair_kernel<256>, TokenPair<256>::kThreads, TokenPair<256>::kRegsNeeded)
+  NQ_CHECK_REGS(token_lane_kernel<128>, TokenLane<128>::kThreads, TokenLane<128>::kRegsNeeded)
+  NQ_CHECK_REGS(token_lane_kernel<192>, TokenLane<192>::kThreads, TokenLane<192>::kRegsNeeded)
+  NQ_CHECK_REGS(token_lane_kernel<256>, TokenLane<256>::kThreads, TokenLane<256>::kRegsNeeded)
+  NQ_CHECK_REGS((weight_lane_kernel<32, true>), (WeightLane<32, true>::kThreads), (WeightLane<32, true>::kRegsNeeded))
+#undef NQ_CHECK_REGS
   return NQ_OK;
 }
 

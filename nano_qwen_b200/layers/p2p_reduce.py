@@ -32,35 +32,29 @@ class P2PRowReducer:
             raise ValueError("peer-memory reduction needs 2..8 ranks")
         self.slot_bytes = (int(slot_bytes) + 255) // 256 * 256
         lib = _cabi.lib()
-        self._own = []
-        mine = {}
-        # a slot holds the message twice over: every 8-byte word is 4 bytes of data + the call number
-        for name, size in (("inbox", 2 * self.tp * 2 * self.slot_bytes), ("state", 256)):
+
+        def alloc(nbytes: int) -> int:
             ptr = ctypes.c_void_p()
-            _cabi.check(lib.nq_p2p_alloc(size, ctypes.byref(ptr)), "nq_p2p_alloc")
-            mine[name] = ptr.value
-            self._own.append(ptr.value)
-        handles = {}
-        for name in ("inbox",):
-            buf = (ctypes.c_ubyte * _HANDLE_BYTES)()
-            _cabi.check(lib.nq_p2p_export(mine[name], buf), "nq_p2p_export")
-            handles[name] = bytes(buf)
+            _cabi.check(lib.nq_p2p_alloc(nbytes, ctypes.byref(ptr)), "nq_p2p_alloc")
+            return ptr.value
+
+        # a slot holds the message twice over: every 8-byte word is 4 bytes of data + the call number
+        inbox = alloc(2 * self.tp * 2 * self.slot_bytes)
+        self._state = alloc(256)
+        handle = (ctypes.c_ubyte * _HANDLE_BYTES)()
+        _cabi.check(lib.nq_p2p_export(inbox, handle), "nq_p2p_export")
         gathered = [None] * self.tp
-        dist.all_gather_object(gathered, handles, group=group)
-        self._mapped = []
-        ptrs = {"inbox": []}
+        dist.all_gather_object(gathered, bytes(handle), group=group)
+        ptrs = []
         for r in range(self.tp):
-            for name in ("inbox",):
-                if r == self.rank:
-                    ptrs[name].append(mine[name])
-                    continue
-                raw = (ctypes.c_ubyte * _HANDLE_BYTES).from_buffer_copy(gathered[r][name])
-                ptr = ctypes.c_void_p()
-                _cabi.check(lib.nq_p2p_import(raw, ctypes.byref(ptr)), "nq_p2p_import")
-                ptrs[name].append(ptr.value)
-                self._mapped.append(ptr.value)
-        self._inbox = (ctypes.c_void_p * self.tp)(*ptrs["inbox"])
-        self._state = mine["state"]
+            if r == self.rank:
+                ptrs.append(inbox)
+                continue
+            raw = (ctypes.c_ubyte * _HANDLE_BYTES).from_buffer_copy(gathered[r])
+            ptr = ctypes.c_void_p()
+            _cabi.check(lib.nq_p2p_import(raw, ctypes.byref(ptr)), "nq_p2p_import")
+            ptrs.append(ptr.value)
+        self._inbox = (ctypes.c_void_p * self.tp)(*ptrs)   # kept for the life of the process (never unmapped)
         dist.barrier(group=group)          # every inbox exists and is zero before anyone pushes
 
     def fits(self, y: torch.Tensor) -> bool:

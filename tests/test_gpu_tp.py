@@ -81,6 +81,30 @@ def _worker(rank, world, port, out_path):
         # same sums up to fp32 summation order (the chunked launches may split K differently)
         err = (piped.float() - single.float()).abs().max() / single.float().abs().max()
         res["pipelined_close_to_single"] = (err <= 8e-3).to(torch.int16).reshape(1)
+        # ---- Qwen3-32B-shaped row layer (down_proj, K = 25600 split over the ranks) against the unsharded product ----
+        K32, N32 = synth.STACKS["qwen3-32b"]["down"]
+        g32 = torch.Generator(device="cuda").manual_seed(4242)            # same seed on every rank: same tensors
+        w32 = (torch.randn(N32, K32, generator=g32, device="cuda") * 0.02).to(torch.bfloat16)
+        wq32, sw32 = ops.weight_quant(w32)
+        del w32
+        torch.set_default_device("cuda")
+        torch.set_default_dtype(torch.bfloat16)
+        row32 = L.RowParallelLinear(K32, N32)
+        torch.set_default_device("cpu")
+        torch.set_default_dtype(torch.float32)
+        row32.weight.weight_loader(row32.weight, wq32)
+        row32.weight_scale_inv.weight_loader(row32.weight_scale_inv, sw32)
+        ok32 = 1
+        for m32 in (1, 64, 2048):
+            x32 = torch.randn(m32, K32, generator=g32, device="cuda").to(torch.bfloat16)
+            full = ops.fp8_linear(x32, wq32, sw32)                         # one GPU, whole K
+            ks = K32 // world
+            part = row32(x32[:, rank * ks:(rank + 1) * ks].contiguous())   # this rank's K-slice + the sum over ranks
+            torch.cuda.synchronize()
+            err = float((part.float() - full.float()).abs().max() / full.float().abs().max())
+            ok32 &= int(err <= 8e-3)                                       # partials are rounded to bf16 before the sum
+        res["row_32b_matches_unsharded"] = torch.tensor([ok32], dtype=torch.int16)
+        del row32, wq32, sw32
         # ---- the peer-memory sum (decode-sized outputs) against NCCL's all-reduce ----
         from nano_qwen_b200.layers import p2p_reduce
         from nano_qwen_b200 import _cabi
@@ -152,6 +176,7 @@ def test_two_gpu_layers_match_the_reference_two_rank_run(tmp_path, built_library
             for name in ("o_proj", "down"):
                 assert np.array_equal(got[r][name], got[r][name + "_graph"]), name     # graph replay == eager
             assert int(got[r]["pipelined_close_to_single"][0]) == 1
+            assert int(got[r]["row_32b_matches_unsharded"][0]) == 1
             assert int(got[r]["p2p_vs_nccl_ok"][0]) == 1
             assert int(got[r]["p2p_graph_replays_ok"][0]) == 1
             assert int(got[r]["device_status"][0]) == 0
