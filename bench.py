@@ -44,9 +44,9 @@ KINDS = ("qkv", "o_proj", "gate_up", "down")
 
 
 # DRAM traffic of the dominant kernel: one ncu capture of its qkv launch at M = 8192 (profiles/
-# token_lane_kernel_qkv_M8192.md) read 77.7 MB and wrote 70.6 MB for 159.4 MB of algorithmic bytes (e4m3 x, e4m3 W,
+# token_lane_kernel_qkv_M8192.md) read 77.4 MB and wrote 70.2 MB for 159.4 MB of algorithmic bytes (e4m3 x, e4m3 W,
 # bf16 y); the other three shapes of the pass are scaled by the same ratio (operands are read once, y is written once).
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 148.3 / 159.4
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 147.6 / 159.4
 
 
 def prefill_gemm_traffic_bytes(layers) -> float:
@@ -491,7 +491,7 @@ def run_gpu_arm(args) -> None:
                                       "bf16 rate); torch._scaled_mm per-tensor FP8 measured 3046 burst / 2618 sustained here",
                          "launches": n_gemm, "avg_launch_us": ms_gemm * 1e3 / max(n_gemm, 1),
                          "traffic": prefill_gemm_traffic_bytes(layers), "traffic_unit": "bytes per launch",
-                         "traffic_note": "ncu dram read+write of the qkv launch (148.3 MB for 159.4 MB algorithmic) "
+                         "traffic_note": "ncu dram read+write of the qkv launch (147.6 MB for 159.4 MB algorithmic) "
                                          "scaled to the mean of the four shapes of the pass"},
             "passes": {"decode_ms": ms_decode, "prefill_ms": ms_prefill, "prefill_gemm_only_ms": ms_gemm,
                        "decode_gemm_only_ms": ms_dec_gemm,

@@ -112,6 +112,25 @@ def test_rmsnorm_quant_matches_oracle(ops, m, h, gemma):
     check_quantised(xq, sx, ref)
 
 
+def test_full_size_producers_sampled_rows(ops):
+    """Prefill-sized inputs (larger than L2): 48 sampled token rows against the oracle."""
+    gen = torch.Generator(device="cuda").manual_seed(31)
+    rows = torch.linspace(0, 8191, 48).long()
+    gu = (torch.randn(8192, 2 * 12288, generator=gen, device="cuda") * 2.0).to(torch.bfloat16)
+    xq, sx = ops.silu_mul_quant(gu)
+    torch.cuda.synchronize()
+    check_quantised(xq[rows.cuda()], sx[rows.cuda()], R.silu_and_mul(gu[rows.cuda()].cpu()))
+    del gu, xq, sx
+    x = (torch.randn(8192, 4096, generator=gen, device="cuda") * 3.0).to(torch.bfloat16)
+    res = torch.randn(8192, 4096, generator=gen, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(4096, generator=gen, device="cuda") * 0.2).to(torch.bfloat16)
+    xq, sx, new_res, _ = ops.rmsnorm_quant(x, w, 1e-6, res, gemma=True)
+    torch.cuda.synchronize()
+    ref, ref_res = R.rms_norm(x[rows.cuda()].cpu(), w.cpu(), 1e-6, res[rows.cuda()].cpu(), gemma=True)
+    assert torch.equal(new_res[rows.cuda()].cpu().view(torch.int16), ref_res.view(torch.int16))
+    check_quantised(xq[rows.cuda()], sx[rows.cuda()], ref)
+
+
 def test_rmsnorm_residual_in_place_through_the_c_abi(ops):
     """residual_out may be the residual_in buffer (what the reference's in-place variant does)."""
     from nano_qwen_b200 import _cabi
