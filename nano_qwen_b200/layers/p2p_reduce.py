@@ -84,17 +84,23 @@ def max_message_bytes(tp: int) -> int:
     return (2 << 20) // max(tp - 1, 1)
 
 
+# Group sizes on which the peer-memory path has been run and checked against NCCL on B200s; it is the default there.
+MEASURED_GROUP_SIZES = (2,)
+
+
 def get_reducer() -> P2PRowReducer | None:
     """The process-wide reducer of the default group, created on first use (a collective call: every rank reaches
-    it in its first row-parallel forward).  ``NQ_P2P_REDUCE=0`` keeps NCCL for every size."""
+    it in its first row-parallel forward).  ``NQ_P2P_REDUCE=0`` keeps NCCL for every size; ``NQ_P2P_REDUCE=1`` turns
+    the peer-memory path on for any group of 2..8 ranks; unset, it is on for the group sizes it has been measured on."""
     global _reducer, _reducer_failed
     if _reducer is not None or _reducer_failed:
         return _reducer
-    if os.environ.get("NQ_P2P_REDUCE", "1") == "0" or not dist.is_initialized() or dist.get_backend() != "nccl":
+    mode = os.environ.get("NQ_P2P_REDUCE", "")
+    if mode == "0" or not dist.is_initialized() or dist.get_backend() != "nccl":
         _reducer_failed = True
         return None
     tp = dist.get_world_size()
-    if not 2 <= tp <= 8:
+    if not 2 <= tp <= 8 or (mode != "1" and tp not in MEASURED_GROUP_SIZES):
         _reducer_failed = True
         return None
     if torch.cuda.is_current_stream_capturing():
