@@ -148,6 +148,8 @@ def test_full_size_8b_layers_sampled_rows_and_linearity(L, name, m):
     assert torch.equal(ops.fp8_linear(x[perm], wq, sw), y[perm])
     # scaling the input by a power of two scales the group scales, not the codes: y doubles exactly
     assert torch.equal(ops.fp8_linear(x * 2, wq, sw).float(), y.float() * 2)
-    # a batch is the concatenation of its halves (tile boundaries do not leak between tokens)
+    # a batch is the concatenation of its halves (tile boundaries do not leak between tokens); a different batch size
+    # may run on a different kernel or K split, i.e. another fp32 summation order: equal up to one bf16 rounding
     h = m // 2 + 3
-    assert torch.equal(torch.cat([ops.fp8_linear(x[:h], wq, sw), ops.fp8_linear(x[h:], wq, sw)]), y)
+    halves = torch.cat([ops.fp8_linear(x[:h], wq, sw), ops.fp8_linear(x[h:], wq, sw)])
+    assert S.max_rel_err(halves.cpu(), y.cpu()) <= 8e-3
