@@ -131,14 +131,9 @@ int gemm_dispatch(const GemmArgs& a, int algo) {
   DeviceCtx* ctx = nullptr;
   st = ensure_init(&ctx);
   if (st != NQ_OK) return st;
-  if (algo == NQ_ALGO_AUTO) {
-    // Measured crossover on B200 (CUDA graph, 8B layer shapes): weight rows on the lanes up to 64 tokens; up to 128
-    // tokens as well when there are few 128-row weight tiles (qkv, o_proj, down: 12-16 us against 17-26 us), not
-    // when there are many (gate_up: 46 us against 27 us).
-    const int64_t n_tiles = (a.N + 127) / 128;
-    const bool weight_lane = a.M <= 64 || (a.M <= 128 && n_tiles * 2 <= ctx->sm_count);
-    algo = weight_lane ? NQ_ALGO_WEIGHT_LANE : NQ_ALGO_TOKEN_LANE;
-  }
+  // Measured crossover on B200 (CUDA graph, 8B layer shapes): weight rows on the lanes up to 64 tokens; at 128 tokens
+  // the token-lane kernel with 128-wide tiles is ahead (71 us against 76 us for the four linears of a layer).
+  if (algo == NQ_ALGO_AUTO) algo = (a.M <= 64) ? NQ_ALGO_WEIGHT_LANE : NQ_ALGO_TOKEN_LANE;
   if (algo == NQ_ALGO_TOKEN_LANE) return launch_gemm_token_lane(a, ctx, 0);
   if (algo == NQ_ALGO_TOKEN_LANE_128) return launch_gemm_token_lane(a, ctx, 128);
   if (algo == NQ_ALGO_TOKEN_LANE_192) return launch_gemm_token_lane(a, ctx, 192);

@@ -1588,14 +1588,14 @@ int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx, int tile_n) {
   if (tile_n == 192) return run_token_lane<192>(a, ctx);
   if (tile_n == 256) return run_token_lane<256>(a, ctx);
   // Measured on B200 (8B-shaped layers): 256-wide tiles are fastest when there is work for every SM (fewest
-  // operand bytes per flop).  128-wide tiles win when the 256-wide tiles are few (up to 64: 256 tokens of qkv,
-  // o_proj, down; 512 tokens of o_proj: 13-23 us against 18-26 us), and when they fill between one and one and a
-  // half rounds of the SMs, where half-size tiles cut the idle tail of the last round (256 tokens of gate_up:
-  // 192 tiles on 148 SMs, 40 us against 43 us).
+  // operand bytes per flop).  128-wide tiles win when twice as many tiles still fit in one round of the SMs
+  // (256-384 tokens of qkv, 256-512 of o_proj and down: 13-23 us against 18-26 us), and when the 256-wide tiles
+  // fill between one and one and a half rounds, where half-size tiles cut the idle tail of the last round
+  // (256 tokens of gate_up: 192 tiles on 148 SMs, 40 us against 43 us).
   if (a.N <= 128) return run_token_lane<128>(a, ctx);
   const int64_t tiles256 = ((a.M + 127) / 128) * ((a.N + 255) / 256);
   const int64_t sm = ctx->sm_count;
-  if (tiles256 <= 64 || (tiles256 > sm && 2 * tiles256 <= 3 * sm)) return run_token_lane<128>(a, ctx);
+  if (2 * tiles256 <= sm || (tiles256 > sm && 2 * tiles256 <= 3 * sm)) return run_token_lane<128>(a, ctx);
   return run_token_lane<256>(a, ctx);
 }
 
