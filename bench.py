@@ -307,7 +307,11 @@ def run_gpu_arm(args) -> None:
         torch.cuda.current_stream().wait_event(copied[i % 2])
         y = run_pass(layers, stage[i % 2])
         consumed[i % 2].record()
-        out_host["prefill"].copy_(y, non_blocking=True)
+        # the result goes back on the copy stream as well, behind the next step's compute
+        y.record_stream(copy_stream)
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[i % 2])
+            out_host["prefill"].copy_(y, non_blocking=True)
         return y
 
     def timed(fn, steps, warmup):
