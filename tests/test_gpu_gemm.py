@@ -155,6 +155,19 @@ def test_known_answers_exact(ops):
         assert torch.all(y.float() == -6.0)
 
 
+
+def test_auto_dispatch_on_seeded_random_shapes(ops):
+    """NQ_ALGO_AUTO picks kernel, tile width and K split from the shape: 40 seeded shapes across those boundaries."""
+    import random
+    rng = random.Random(20240607)
+    for i in range(40):
+        m = rng.choice([1, 5, 33, 64, 65, 100, 128, 129, 200, 256, 257, 384, 500, 600])
+        n = rng.choice([8, 72, 128, 136, 256, 520, 1024, 1536, 2048])
+        k = rng.choice([16, 128, 144, 512, 1024, 2048])
+        case = make_case(m, n, k, seed=1000 + i, bias=bool(i & 1))
+        check(run_gemm(ops, case, ops.ALGO_AUTO), case)
+
+
 def test_results_are_deterministic(ops):
     case = make_case(48, 1024, 4096, seed=5)
     a = run_gemm(ops, case, ops.ALGO_WEIGHT_LANE, split_k=4)
