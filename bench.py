@@ -75,7 +75,7 @@ def measured_peaks() -> dict:
 # --------------------------------------------------------------------------- #
 # CPU arm: the oracle (port of the reference path) timed on the host cores     #
 # --------------------------------------------------------------------------- #
-def cpu_reference_sample(repeats: int, m_decode: int = 256, m_prefill: int = 1024) -> dict:
+def cpu_reference_sample(repeats: int, m_decode: int = 256, m_prefill: int = 8192) -> dict:
     """Times ONE layer of the stack on the CPU: dynamic activation quantisation, dequantisation of
     both operands to fp32 and the reference's ``F.linear`` (fp32), bf16 out — for a decode pass of
     ``m_decode`` tokens and a prefill chunk of ``m_prefill`` tokens.  Returns TFLOP/s."""
@@ -106,7 +106,7 @@ def cpu_reference_sample(repeats: int, m_decode: int = 256, m_prefill: int = 102
     flops = FLOPS_PER_TOKEN_LAYER * (m_decode + m_prefill)
     best = min(times)
     return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"1 of {LAYERS} layers, decode M={m_decode} + prefill chunk M={m_prefill} "
+            "sample": f"1 of {LAYERS} layers, decode M={m_decode} + prefill M={m_prefill} "
                       f"(act quant + dequant + fp32 F.linear), best of {repeats}, {best:.2f} s",
             "seconds": best, "host_cpus": os.cpu_count()}
 
@@ -499,7 +499,7 @@ def run_gpu_arm(args) -> None:
         decode_gbs = LAYERS * layer_bytes / (ms_decode * 1e-3) / 1e9
         in_bytes = sum(t.numel() * 2 for d in host.values() for t in d.values())
         out_bytes = sum(t.numel() * 2 for t in out_host.values())
-        cpu = cpu_reference_sample(2) if world == 1 else None
+        cpu = cpu_reference_sample(5) if world == 1 else None
         line = {
             "metric": "fp8_linear_stack_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
