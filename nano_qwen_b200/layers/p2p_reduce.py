@@ -85,7 +85,7 @@ def max_message_bytes(tp: int) -> int:
 
 
 # Group sizes on which the peer-memory path has been run and checked against NCCL on B200s; it is the default there.
-MEASURED_GROUP_SIZES = (2, 4)
+MEASURED_GROUP_SIZES = (2, 4, 8)
 
 
 def get_reducer() -> P2PRowReducer | None:
