@@ -41,11 +41,13 @@ M_DECODE, M_PREFILL = 256, 8192
 # 2 * sum(N*K) over the four linears of one layer
 FLOPS_PER_TOKEN_LAYER = 2 * (HIDDEN * (HEADS + 2 * KV_HEADS) * HEAD_DIM + HIDDEN * HIDDEN + HIDDEN * 2 * INTER + INTER * HIDDEN)
 KINDS = ("qkv", "o_proj", "gate_up", "down")
+WORKLOAD = ("Qwen3-8B-shaped 36-layer FP8 linear stack: decode pass M=256 (CUDA graph) + "
+            "chunked-prefill pass M=8192 per step")
 
 
-# DRAM traffic of the dominant kernel: one ncu capture of its qkv launch at M = 8192 (profiles/
-# token_lane_kernel_qkv_M8192.md) read 77.4 MB and wrote 70.2 MB for 159.4 MB of algorithmic bytes (e4m3 x, e4m3 W,
-# bf16 y); the other three shapes of the pass are scaled by the same ratio (operands are read once, y is written once).
+# DRAM traffic of the dominant kernel: one ncu capture of its qkv launch at M = 8192 read 77.4 MB and wrote 70.2 MB
+# for 159.4 MB of algorithmic bytes (e4m3 x, e4m3 W, bf16 y); the other three shapes of the pass are scaled by the
+# same ratio (operands are read once, y is written once).
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 147.6 / 159.4
 
 
@@ -80,6 +82,9 @@ def cpu_reference_sample(repeats: int, m_decode: int = 256, m_prefill: int = 819
     both operands to fp32 and the reference's ``F.linear`` (fp32), bf16 out — for a decode pass of
     ``m_decode`` tokens and a prefill chunk of ``m_prefill`` tokens.  Returns TFLOP/s."""
     from oracle import fp8_spec as S, ref_linear as R
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; this arm is the only work on the host
+    # (the other ranks have left), so it takes every core at every N.
+    torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
     shapes = {"qkv": (HIDDEN, (HEADS + 2 * KV_HEADS) * HEAD_DIM), "o_proj": (HIDDEN, HIDDEN),
               "gate_up": (HIDDEN, 2 * INTER), "down": (INTER, HIDDEN)}
@@ -125,8 +130,8 @@ def run_reference_arm(args) -> None:
         "impl": "reference", "metric": "fp8_linear_stack_tflops", "value": res["value"], "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": res["seconds"] * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "Qwen3-8B-shaped 36-layer FP8 linear stack, decode M=256 + prefill M=8192 per step "
-                               "(CPU arm: bounded sample, see cpu_baseline.sample)", "tp": args.gpus},
+        "config": {"workload": WORKLOAD, "tp": args.gpus, "layers": LAYERS,
+                   "l2": "weights of the stack (6.95 GB / tp) exceed L2; no flush needed"},
         "cpu_baseline": res,
         "e2e": {"value": res["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": wall,
@@ -143,7 +148,8 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.path = tempfile.mktemp(suffix=".csv")
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
         self.proc = None
         self.gpu_index = gpu_index
 
@@ -181,6 +187,49 @@ class ClockSampler:
         hot.sort()
         return {"sm_mhz": hot[len(hot) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons),
                 "power_w_max": max(power), "samples": len(sm)}
+
+
+class NvmlClock:
+    """SM clock read through NVML (read-only queries) from a host thread while a short window is timed; the
+    nvidia-smi sampler above needs a few hundred milliseconds to start, too long for a 30 ms window."""
+
+    def __init__(self, gpu_index: int):
+        self.samples, self.handle, self._stop = [], None, threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = [v for v in visible.split(",") if v.strip().isdigit()]
+            phys = int(ids[gpu_index]) if gpu_index < len(ids) else gpu_index
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self._read = lambda: pynvml.nvmlDeviceGetClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.handle = None
+
+    def __enter__(self):
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+        return self
+
+    def _loop(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self._read())
+            except Exception:
+                return
+            time.sleep(0.004)
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self.handle is not None:
+            self.thread.join()
+
+    def median(self):
+        if not self.samples:
+            return None
+        v = sorted(self.samples)
+        return v[len(v) // 2]
 
 
 # Qwen3-32B-shaped layer (config 4 of the contract): hidden, heads, kv heads, head dim, intermediate
@@ -339,10 +388,21 @@ def run_gpu_arm(args) -> None:
     ms_step, launches = timed(step_resident, args.steps, args.warmup)
     launches += graph_kernels * args.steps                   # replays launch the captured kernels without host calls
     clocks = sampler.stop() if rank == 0 else None
-    ms_e2e, _ = timed(step_e2e, max(1, min(args.steps, 5)), 1)
+    ms_e2e, _ = timed(step_e2e, args.steps, args.warmup)
+    torch.cuda.synchronize()                                 # the copy stream's last prefetch has landed
 
     # ---- per-pass and per-kernel timings that explain the headline (same device, after the timed region) ----
-    ms_decode, _ = timed(graph.replay, 5, 2)
+    # The decode pass is short kernels whose time follows the SM clock: right behind the power-capped prefill steps
+    # the clock is still low, after a pause it is at its maximum.  Both windows are sampled so that the two figures
+    # (this one and detail.decode["256"]) can be compared as time x clock.
+    def timed_with_clock(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        with NvmlClock(local) as clk:
+            ms, _ = timed(fn, steps, 0)
+        return ms, clk.median()
+
+    ms_decode, mhz_decode = timed_with_clock(graph.replay, 40, 5)
     ms_prefill, _ = timed(lambda: run_pass(layers, dev["prefill"]), 3, 1)
     # dominant kernel: the token-lane GEMM of the prefill pass, timed alone on pre-quantised activations
     pre = {name: ops.act_quant(dev["prefill"][name]) for name in KINDS}
@@ -388,10 +448,10 @@ def run_gpu_arm(args) -> None:
                 gm = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gm):
                     run_pass(layers, xs)
-                ms, _ = timed(gm.replay, 5, 2)
+                ms, mhz = timed_with_clock(gm.replay, 20, 3)
                 del gm
             else:
-                ms, _ = timed(lambda: run_pass(layers, xs), 2, 1)
+                ms, mhz = timed_with_clock(lambda: run_pass(layers, xs), 2, 1)
             shapes_m = {"qkv": (HIDDEN, (HEADS + 2 * KV_HEADS) * HEAD_DIM // tp), "o_proj": (HIDDEN // tp, HIDDEN),
                         "gate_up": (HIDDEN, 2 * INTER // tp), "down": (INTER // tp, HIDDEN)}
             bytes_layer = sum(2 * m * k + n * k + 4 * ((n + 127) // 128) * ((k + 127) // 128) + 2 * m * n
@@ -401,6 +461,7 @@ def run_gpu_arm(args) -> None:
                 "layer_us": round(layer_us, 2),
                 "tflops": round(FLOPS_PER_TOKEN_LAYER * m / (layer_us * 1e-6) / 1e12, 1),          # whole job
                 "hbm_gbs_per_gpu": round(bytes_layer / (layer_us * 1e-6) / 1e9, 1),
+                "sm_mhz": mhz,
             }
             del xs
         torch.cuda.synchronize()
@@ -505,8 +566,7 @@ def run_gpu_arm(args) -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)",
             "data": "synthetic",
-            "config": {"workload": "Qwen3-8B-shaped 36-layer FP8 linear stack: decode pass M=256 (CUDA graph) + "
-                                   "chunked-prefill pass M=8192 per step", "tp": tp, "layers": LAYERS,
+            "config": {"workload": WORKLOAD, "tp": tp, "layers": LAYERS,
                        "l2": "weights of the stack (6.95 GB / tp) exceed L2; no flush needed"},
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
@@ -523,7 +583,8 @@ def run_gpu_arm(args) -> None:
                                          "scaled to the mean of the four shapes of the pass"},
             "passes": {"decode_ms": ms_decode, "prefill_ms": ms_prefill, "prefill_gemm_only_ms": ms_gemm,
                        "decode_gemm_only_ms": ms_dec_gemm,
-                       "decode_layer_us": ms_decode * 1e3 / LAYERS, "prefill_layer_us": ms_prefill * 1e3 / LAYERS,
+                       "decode_layer_us": ms_decode * 1e3 / LAYERS, "decode_sm_mhz": mhz_decode,
+                       "prefill_layer_us": ms_prefill * 1e3 / LAYERS,
                        "decode_hbm_gbs": decode_gbs, "decode_hbm_frac_of_measured": decode_gbs / peaks["hbm_gbs"],
                        "prefill_tflops": LAYERS * FLOPS_PER_TOKEN_LAYER * M_PREFILL / (ms_prefill * 1e-3) / 1e12},
             "detail": {"note": "one pass of the same stack per batch size M: act quant + GEMM (+ all-reduce) per linear; "
@@ -536,14 +597,26 @@ def run_gpu_arm(args) -> None:
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
-    # Graphs that captured NCCL collectives keep the communicator busy: drop them before tearing it down,
-    # and do not let a slow communicator teardown turn a finished benchmark into a hang.
-    del graph, g2
+    # Normal interpreter exit (at-exit hooks run).  Graphs that captured collectives pin the communicator: drop
+    # them first, then tear the group down.  A watchdog only guards against a teardown that never returns.
+    del graph, g2, y_decode
+    import gc
+    gc.collect()
     torch.cuda.synchronize()
     dist.barrier()
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(0)
+
+    def _give_up():
+        sys.stderr.write("bench.py: process-group teardown did not return within 60 s; leaving without it\n")
+        sys.stderr.flush()
+        os._exit(0)
+
+    watchdog = threading.Timer(60.0, _give_up)
+    watchdog.daemon = True
+    watchdog.start()
+    dist.destroy_process_group()
+    watchdog.cancel()
 
 
 def main():

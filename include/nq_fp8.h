@@ -50,7 +50,7 @@ extern "C" {
 #define NQ_OK 0
 #define NQ_ERR_BAD_ARGUMENT (-1)   /* null pointer, negative size, misaligned pointer or stride */
 #define NQ_ERR_UNSUPPORTED (-2)    /* shape outside what the kernels cover */
-#define NQ_ERR_WORKSPACE (-3)      /* workspace missing or smaller than nq_fp8_gemm_workspace_bytes */
+#define NQ_ERR_WORKSPACE (-3)      /* a size limit of a fixed buffer is exceeded (noalloc scratch, p2p slot) */
 #define NQ_ERR_CUDA (-4)           /* a CUDA runtime/driver call failed (see nq_last_cuda_error) */
 #define NQ_ERR_DEVICE_TIMEOUT (-5) /* a bounded device-side wait expired (reported by nq_device_status) */
 #define NQ_ERR_NOT_SM100 (-6)      /* the current device is not compute capability 10.x */
@@ -71,6 +71,10 @@ extern "C" {
 
 /* ABI version of this header (major*100 + minor). */
 int nq_version(void);
+
+/* Hash of the CUDA sources and headers this binary was compiled from (set by the build script; "unknown" for a
+ * hand-made build).  Lets a host check that a shipped binary matches the source tree it sits in. */
+const char* nq_source_hash(void);
 
 /* Human-readable name of a status code (static storage, never NULL). */
 const char* nq_status_string(int status);
@@ -116,10 +120,10 @@ int nq_rmsnorm_quant_e4m3_g128(const void* x, const void* residual_in, const voi
                                void* y_out, int64_t ldy,
                                void* xq, int64_t ld_xq, float* sx, int64_t ld_sx, void* stream);
 
-/* Bytes of zero-initialised scratch the GEMM may need for this problem.
- * The buffer must be zero-filled ONCE by the caller before its first use; the
- * library leaves it in a reusable state after every launch.  Two launches that
- * may overlap on the GPU (different streams) need different buffers. */
+/* Bytes of global scratch the GEMM needs for this problem: always 0.  Every kernel of this library keeps its
+ * split-K partial sums in shared memory (exchanged across a thread-block cluster), so the `workspace` /
+ * `workspace_bytes` arguments below are accepted and ignored (pass NULL, 0).  The query stays in the ABI so that a
+ * caller written against it keeps working if a later kernel does need scratch. */
 size_t nq_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 /* y = bf16( sum_t sx[t,m] * sw[n/128,t] * (xq[m, tile t] . wq[n, tile t]) + bias[n] ),

@@ -21,6 +21,7 @@ FUSED_MAX_TOKENS, FUSED_AUTO_TOKENS = 32, 8      # NQ_FUSED_MAX_TOKENS, NQ_FUSED
 # name -> (restype, argtypes); every symbol include/nq_fp8.h declares
 SIGNATURES = {
     "nq_version": (c_int, []),
+    "nq_source_hash": (c_char_p, []),
     "nq_status_string": (c_char_p, [c_int]),
     "nq_last_cuda_error": (c_char_p, []),
     "nq_init": (c_int, []),

@@ -4,6 +4,7 @@
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -20,22 +21,42 @@ NVCC_FLAGS = [
 ]
 
 
-def _stale() -> bool:
+def source_hash() -> str:
+    """sha256 over the CUDA sources and headers the library is built from (names and contents, fixed order)."""
+    h = hashlib.sha256()
+    for f in SOURCES + HEADERS:
+        h.update(os.path.basename(f).encode() + b"\0")
+        with open(os.path.join(CSRC, f), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:32]
+
+
+def built_hash() -> str | None:
+    """The source hash compiled into the existing library (``nq_source_hash``), or None if there is no usable library."""
     if not os.path.exists(LIB_PATH):
-        return True
-    built = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
-    return any(os.path.getmtime(d) > built for d in deps)
+        return None
+    import ctypes
+    try:
+        lib = ctypes.CDLL(LIB_PATH)
+        fn = lib.nq_source_hash
+    except (OSError, AttributeError):
+        return None
+    fn.restype = ctypes.c_char_p
+    return fn().decode()
+
+
+def _stale() -> bool:
+    return built_hash() != source_hash()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles the library if it is missing or older than its sources; returns its path."""
+    """Compiles the library unless the one in the tree was built from exactly the present sources; returns its path."""
     if not force and not _stale():
         return LIB_PATH
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: cannot build libnq_fp8.so")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, *SOURCES]
+    cmd = [nvcc, *NVCC_FLAGS, f'-DNQ_SOURCE_HASH="{source_hash()}"', "-o", LIB_PATH, *SOURCES]
     proc = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
     if verbose or proc.returncode != 0:
         sys.stderr.write(proc.stdout + proc.stderr)

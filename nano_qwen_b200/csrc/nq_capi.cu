@@ -39,9 +39,9 @@ int ensure_init(DeviceCtx** out) {
   if (e != cudaSuccess) return check_cuda(e);
   if (dev < 0 || dev >= kMaxDevices) return NQ_ERR_UNSUPPORTED;
   DeviceCtx* c = &g_ctx[dev];
-  if (!c->ready) {
+  if (!c->ready.load(std::memory_order_acquire)) {
     std::lock_guard<std::mutex> lock(g_mu);
-    if (!c->ready) {
+    if (!c->ready.load(std::memory_order_relaxed)) {
       int major = 0;
       e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
       if (e != cudaSuccess) return check_cuda(e);
@@ -70,7 +70,7 @@ int ensure_init(DeviceCtx** out) {
       c->status_dev = static_cast<DeviceStatus*>(devp);
       const int st = setup_gemm_kernels();
       if (st != NQ_OK) return st;
-      c->ready = true;
+      c->ready.store(true, std::memory_order_release);
     }
   }
   *out = c;
@@ -147,12 +147,16 @@ int gemm_dispatch(const GemmArgs& a, int algo) {
 }  // namespace
 }  // namespace nq
 
-namespace nq { extern long long* g_prof_buffer; }
 using namespace nq;
 
 extern "C" {
 
 int nq_version(void) { return 100; }
+
+#ifndef NQ_SOURCE_HASH
+#define NQ_SOURCE_HASH "unknown"
+#endif
+const char* nq_source_hash(void) { return NQ_SOURCE_HASH; }
 
 const char* nq_status_string(int status) {
   switch (status) {
@@ -218,6 +222,7 @@ int nq_fp8_linear(const void* x, int64_t ldx, const void* wq, int64_t ld_wq, con
                   float* sx_scratch, void* workspace, size_t workspace_bytes, int algo, int split_k, void* stream) {
   if (M < 0 || N < 0 || K < 0) return NQ_ERR_BAD_ARGUMENT;
   if (M == 0 || N == 0) return NQ_OK;
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return NQ_ERR_UNSUPPORTED;   // before the quantiser runs
   const int64_t ld_xq = (K + 15) / 16 * 16;
   const int64_t ld_sx = (M + 3) / 4 * 4;
   // A handful of tokens: quantise inside the weight-lane GEMM (one launch, no xq / sx round trip) when the rows
@@ -276,10 +281,5 @@ int nq_set_sm_reserve(int n) {
 }
 
 int64_t nq_launch_count(void) { return g_launches.load(); }
-
-#ifdef NQ_PROFILE
-// Profiling builds only: device buffer of [grid][16] cycle counters, or null to switch accounting off.
-void nq_debug_profile_buffer(long long* device_buffer) { nq::g_prof_buffer = device_buffer; }
-#endif
 
 }  // extern "C"

@@ -25,23 +25,8 @@
 #include "nq_internal.cuh"
 #include <type_traits>
 
-// Optional cycle accounting per role (compiled in with -DNQ_PROFILE only).
-#ifdef NQ_PROFILE
-#define NQ_PROF_DECL long long pt_[4] = {0, 0, 0, 0}; long long pt0_ = clock64();
-#define NQ_PROF_ADD(i) { const long long t_ = clock64(); pt_[i] += t_ - pt0_; pt0_ = t_; }
-#define NQ_PROF_STORE(base) if (p.prof) { for (int i_ = 0; i_ < 4; ++i_) p.prof[blockIdx.x * 16 + (base) + i_] = pt_[i_]; }
-// event trace of CTA 0: p.prof[148*16 + ev*512 + (it & 511)] = clock
-#define NQ_TRACE(ev, it) if (p.prof && blockIdx.x == 0 && (it) < 512) p.prof[148 * 16 + (ev) * 512 + (it)] = clock64();
-#else
-#define NQ_TRACE(ev, it)
-#define NQ_PROF_DECL
-#define NQ_PROF_ADD(i)
-#define NQ_PROF_STORE(base)
-#endif
 
 namespace nq {
-
-long long* g_prof_buffer = nullptr;   // device buffer [grid][16], set by nq_debug_profile_buffer (profiling builds)
 
 namespace {
 
@@ -140,7 +125,6 @@ struct TokenLaneParams {
   int y_vec;                  // 1: 16-byte stores are legal for y
   int y_tma;                  // 1: the output tensor map is valid (y 16-byte aligned, row stride a multiple of 16 bytes)
   int sx_vec;                 // 1: 16-byte loads of sx rows are legal
-  long long* prof;            // cycle accounting buffer (profiling builds) or null
   uint32_t wait_mode;         // 0 try_wait, 1 test_wait spin, >1 try_wait with that suspend hint (ns)
   DeviceStatus* status;
   uint64_t wait_limit_ns;
@@ -249,23 +233,19 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      NQ_PROF_DECL
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int m_t, n_t;
         token_lane_tile_coords<BN>(tile, num_m, num_n, m_t, n_t);
         for (int kt = kt0; kt < kt1; ++kt, ++it) {
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
-          NQ_PROF_ADD(1)
           if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteProdEmpty, kt)) { ok = false; break; }
-          NQ_PROF_ADD(0)
           uint8_t* a = smem + s * C::kStageBytes;
           mbar_arrive_expect_tx(&bars->full[s], C::kStageBytes);
           tma_load_2d(a, &tm_x, &bars->full[s], kt * kTileK, m_t * 128);
           tma_load_2d(a + kLaneTileBytes, &tm_w, &bars->full[s], kt * kTileK, n_t * BN);
         }
       }
-      NQ_PROF_STORE(0)
       if (!ok) drain_after_abort(bars, C::kStages, it);
     }
    } else if (warp == 1 || warp == 3) {
@@ -280,13 +260,11 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       const uint32_t mine = (warp == 1) ? 0u : 1u;
       uint32_t it = 0;
       bool ok = true;
-      NQ_PROF_DECL
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         for (int kt = kt0; kt < kt1; ++kt, ++it) {
           if ((it & 1u) != mine) continue;
           const int b = it % C::kNumAcc;
           const uint32_t aph = (it / C::kNumAcc) & 1;
-          NQ_PROF_ADD(2)
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
           const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
@@ -294,21 +272,15 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
           const uint32_t d = tmem_base + b * C::kAccStride;
           if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
-          NQ_PROF_ADD(0)
-          NQ_TRACE(0, it)
           if (!mbar_wait(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
-          NQ_PROF_ADD(1)
-          NQ_TRACE(1, it)
           tc_fence_after_sync();
 #pragma unroll
           for (int k = 0; k < kTileK / 32; ++k)   // 32 bytes of K per UMMA: +2 in the (addr >> 4) field
             umma_f8(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
           umma_commit(&bars->empty[s]);
           umma_commit(&bars->tmem_full[b]);
-          NQ_TRACE(2, it)
         }
       }
-      if (warp == 1) { NQ_PROF_STORE(4) }
       if (!ok) {   // let MMAs already issued finish before TMEM is freed
         uint64_t* td = (warp == 1) ? &bars->teardown : &bars->teardown2;
         umma_commit(td);
@@ -398,7 +370,6 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     float acc[C::kCols];
     uint32_t it = 0;
     bool ok = true;
-    NQ_PROF_DECL
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int m_t, n_t;
       token_lane_tile_coords<BN>(tile, num_m, num_n, m_t, n_t);
@@ -409,10 +380,7 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       for (int kt = kt0; kt < kt1; ++kt, ++it) {
         const int b = it % C::kNumAcc;
         const uint32_t aph = (it / C::kNumAcc) & 1;
-        NQ_PROF_ADD(2)
         if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt)) { ok = false; break; }
-        NQ_PROF_ADD(0)
-        if (lane == 0) { NQ_TRACE(3 + 2 * (warp - C::kFirstEpiWarp), it) }
         tc_fence_after_sync();
         const float s = scale_ring[(b * C::kEpiGroups + h) * 128 + row];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * C::kAccStride + h * C::kCols;
@@ -434,13 +402,10 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
-        NQ_PROF_ADD(1)
-        if (lane == 0) { NQ_TRACE(4 + 2 * (warp - C::kFirstEpiWarp), it) }
         promote32(acc + C::kCols - 64, ra, s);
         promote32(acc + C::kCols - 32, rb, s);
       }
       if (!ok) break;
-      NQ_PROF_ADD(2)
       if (p.splits > 1) {
         // K-split launch: the partial tile goes to shared memory (the drained pipeline stages) for the
         // cluster-wide sum below.  Row stride 260 floats keeps 16-byte stores of a quarter-warp apart.
@@ -511,14 +476,9 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           }
         }
       }
-      NQ_PROF_ADD(3)
     }
     // shared memory must stay valid until the last bulk stores have read it (and y must be complete)
     if (C::kTmaStore && p.y_tma && lane == 0) tma_store_wait_all<0>();
-#ifdef NQ_PROFILE
-    if (warp == C::kFirstEpiWarp && lane == 0) { NQ_PROF_STORE(8) }
-    if (warp == C::kFirstEpiWarp + 7 && lane == 0) { NQ_PROF_STORE(12) }
-#endif
   }
 
   if (p.splits > 1) {
@@ -931,18 +891,10 @@ struct WeightLaneParams {
   int y_vec;                  // 1: 8-byte stores are legal for y
   const __nv_bfloat16* x;     // FUSED kernels: unquantised activations [M, K], row stride ldx (16-byte aligned rows)
   int64_t ldx;
-  long long* prof;            // phase timestamps (profiling builds) or null
   DeviceStatus* status;
   uint64_t wait_limit_ns;
 };
 
-#ifdef NQ_PROFILE
-#define NQ_WL_STAMP(i) if (p.prof && threadIdx.x == (i == 1 || i == 2 ? 32 : 128)) p.prof[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = globaltimer_ns();
-#define NQ_QTRACE(ev, it) if (p.prof && blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) p.prof[4096 * 8 + (ev) * 64 + (it)] = clock64();
-#else
-#define NQ_WL_STAMP(i)
-#define NQ_QTRACE(ev, it)
-#endif
 
 // acc[0..16) += r[0..16) * sc[0..16)   (sc in shared memory, read as four broadcast float4; packed two-wide FMAs)
 __device__ __forceinline__ void promote16_cols(float* acc, const uint32_t* r, const float* sc) {
@@ -1091,7 +1043,6 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   const int nkt = kt1 - kt0;
   const uint32_t stage_tx = FUSED ? kLaneTileBytes : kLaneTileBytes + p.tok_box * kTileK;
   const int pre = min(nkt, C::kStages);                   // weight tiles requested before anything else
-  NQ_WL_STAMP(0)
 
   if (threadIdx.x == 0) {
     // a stage is full when the weight tile has landed (and, fused, its quantiser warp has written the activations);
@@ -1167,9 +1118,6 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const int s = i % C::kStages;
         const uint32_t ph = (i / C::kStages) & 1;
         if (!mbar_wait(&bars->full[s], ph, ac, kSiteWeightLane + kSiteMmaFull, i)) { ok = false; break; }
-        if (i == 0) { NQ_WL_STAMP(1) }
-        if (i == nkt - 1) { NQ_WL_STAMP(2) }
-        NQ_QTRACE(5, i)
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
         const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
@@ -1243,7 +1191,6 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           const uint32_t aph = (i / C::kNumAcc) & 1;
           if (!mbar_wait(&bars->empty[s], ph ^ 1, ac, kSiteWeightLane + kSiteProdEmpty, i) ||
               !mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteWeightLane + kSiteScaleEmpty, i)) { ok = false; break; }
-          if (lane == 0) { NQ_QTRACE(0, i) }
           if (i < (C::kStages > C::kNumAcc ? C::kStages : C::kNumAcc)) {
             // rows between the last token pair and the UMMA's N extent: zeros, written on the first pass over the rings
             for (int pz = npairs; pz * 2 < n_umma; ++pz) {
@@ -1278,13 +1225,11 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         else if (n == 2) convert(std::integral_constant<int, 2>{});
         else convert(std::integral_constant<int, 1>{});
         if (hh == upt - 1) {
-          if (lane == 0) { NQ_QTRACE(1, i) }
           fence_proxy_async_smem();                         // generic-proxy writes -> visible to the tensor core
           __syncwarp();
           if (lane == 0) {
             mbar_arrive(&bars->full[s]);
             mbar_arrive(&bars->tmem_full[b]);
-            NQ_QTRACE(2, i)
           }
         }
         advance(cur);
@@ -1302,7 +1247,6 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const int b = i % C::kNumAcc;
       const uint32_t aph = (i / C::kNumAcc) & 1;
       if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteWeightLane + kSiteEpiTmemFull, i)) { epi_ok = false; break; }
-      if (threadIdx.x == 128) { NQ_QTRACE(3, i) }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * TOK + col0;
       const float* scb = sc + b * TOK + col0;
@@ -1324,14 +1268,11 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty[b]);
-      if (threadIdx.x == 128) { NQ_QTRACE(4, i) }
     }
 
     // All MMAs of this CTA have completed (the epilogue waited for the last
     // accumulator), so the pipeline stages are free: reuse them for the exchange.
-    NQ_WL_STAMP(3)
     __syncthreads();
-    NQ_WL_STAMP(4)
     float* xch = reinterpret_cast<float*>(smem);              // [TOK][128] fp32, weight row fastest
     {
       const int nrow = q * 32 + lane;
@@ -1340,7 +1281,6 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         if (col0 + c < n_umma) xch[(col0 + c) * 128 + nrow] = epi_ok ? acc[c] : 0.0f;
     }
     cluster_sync_all();   // partial tiles of all splits are visible cluster-wide
-    NQ_WL_STAMP(5)
 
     if (bars->abort_flag == 0) {
       // This CTA sums tokens z, z+splits, ... over all splits in rank order (fixed
@@ -1403,9 +1343,7 @@ weight_lane_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
       }
     }
-    NQ_WL_STAMP(6)
     cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
-    NQ_WL_STAMP(7)
   }
 
   tc_fence_before_sync();
@@ -1485,7 +1423,6 @@ int run_token_lane(const GemmArgs& a, DeviceCtx* ctx) {
     p.y_tma = 1;
   }
   p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
-  p.prof = g_prof_buffer;
   p.wait_mode = 0;
   p.status = ctx->status_dev;
   p.wait_limit_ns = wait_limit_ns();
@@ -1519,7 +1456,6 @@ int run_token_pair(const GemmArgs& a, DeviceCtx* ctx) {
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
   p.y_tma = 0;
   p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
-  p.prof = nullptr;
   p.wait_mode = 0;
   p.status = ctx->status_dev;
   p.wait_limit_ns = wait_limit_ns();
@@ -1564,7 +1500,6 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
   p.M = static_cast<int>(a.M); p.N = static_cast<int>(a.N); p.K = static_cast<int>(a.K);
   p.splits = splits;
   p.wait_mode = 0;
-  p.prof = g_prof_buffer;
   p.tok_box = tokens_box;
   p.y_vec = (a.ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 8 == 0);
   p.status = ctx->status_dev;

@@ -2,12 +2,13 @@
 #pragma once
 #include "../../include/nq_fp8.h"
 #include "nq_ptx.cuh"
+#include <atomic>
 
 namespace nq {
 
 // Per-device state created by ensure_init().
 struct DeviceCtx {
-  bool ready = false;
+  std::atomic<bool> ready{false};   // set last, with release order; read with acquire before the other fields
   int sm_count = 0;
   DeviceStatus* status_host = nullptr;  // mapped pinned host memory
   DeviceStatus* status_dev = nullptr;   // device alias of the same block

@@ -48,6 +48,8 @@ extern "C" int nq_fp8_linear_noalloc(const void* x, int64_t ldx, const void* wq,
                                      int64_t K, int algo, int split_k, void* stream) {
   if (M < 0 || N < 0 || K < 0) return NQ_ERR_BAD_ARGUMENT;
   if (M == 0 || N == 0) return NQ_OK;
+  // sizes the GEMM would refuse anyway; checked first so that the products below cannot wrap around
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return NQ_ERR_UNSUPPORTED;
   const int64_t ld_xq = (K + 15) / 16 * 16;
   const int64_t ld_sx = (M + 3) / 4 * 4;
   const int64_t groups = (K + 127) / 128;

@@ -5,8 +5,9 @@
 // when the output is small enough that the collective is bound by latency, not bandwidth.
 //
 // One-shot push protocol with the flag inside the data (no fence, no second trip over the link).  Every rank owns an
-// inbox of 2 parities x tp senders x (2 x slot_bytes), reachable by all peers.  Call number e (a counter kept in
-// device memory, so that a CUDA graph replays correctly; never 0) works on parity e & 1:
+// inbox of 2 parities x tp senders x (2 x slot_bytes), reachable by all peers.  The calls are counted by a 64-bit
+// number n kept in device memory (so that a CUDA graph replays correctly); call n works on parity n & 1 and tags
+// its words with e = n mod (2^32 - 1) + 1, which is never 0, the value of a word that was never written:
 //   1. each thread turns 16 bytes of this rank's partial into four 8-byte words {4 bytes of data, e} and stores
 //      them into slot [e & 1][rank] of every peer's inbox (8-byte stores are atomic: a word is either old or new),
 //   2. then polls (bounded) the same positions of its own inbox until every word carries e, and adds the tp
@@ -35,7 +36,7 @@ struct RowReduceParams {
   uint8_t* inbox[kMaxRanks];    // inbox base of every rank (own entry: local address)
   int rank, tp;
   int64_t slot_bytes;           // payload capacity of a slot (it occupies twice that)
-  uint32_t* state;              // [0] calls completed so far, [1] block ticket of the call in flight
+  uint64_t* state;              // [0] calls completed so far (64 bits), [1] low half: block ticket of the call in flight
   DeviceStatus* status;
   uint64_t limit_ns;
 };
@@ -71,9 +72,10 @@ __global__ void __launch_bounds__(kThreads) row_reduce_p2p_kernel(const RowReduc
   const int b = blockIdx.x, tid = threadIdx.x;
   if (tid == 0) s_abort = 0;
   __syncthreads();
-  const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.state) + 1u;   // number of this call, 1-based
+  const uint64_t call = *reinterpret_cast<volatile uint64_t*>(p.state) + 1ull;   // number of this call, 1-based
+  const uint32_t e = static_cast<uint32_t>(call % 0xFFFFFFFFull) + 1u;           // tag in the words: 1 .. 2^32 - 1
   const int64_t slot2 = 2 * p.slot_bytes;
-  const int64_t par_off = static_cast<int64_t>(e & 1u) * p.tp;
+  const int64_t par_off = static_cast<int64_t>(call & 1ull) * p.tp;
   const int64_t per = (p.n16 + gridDim.x - 1) / gridDim.x;
   const int64_t lo = b * per, hi = min(lo + per, p.n16);
 
@@ -128,11 +130,12 @@ __global__ void __launch_bounds__(kThreads) row_reduce_p2p_kernel(const RowReduc
   // the last block to finish closes the call
   __syncthreads();
   if (tid == 0) {
-    const uint32_t t = atomicAdd(p.state + 1, 1u);
+    uint32_t* ticket = reinterpret_cast<uint32_t*>(p.state + 1);
+    const uint32_t t = atomicAdd(ticket, 1u);
     if (t == gridDim.x - 1) {
-      p.state[1] = 0u;
+      *ticket = 0u;
       __threadfence();
-      *reinterpret_cast<volatile uint32_t*>(p.state) = e;
+      *reinterpret_cast<volatile uint64_t*>(p.state) = call;
     }
   }
 }
@@ -212,7 +215,7 @@ int nq_row_reduce_p2p(const void* partial, void* y, int64_t count, void* const* 
   p.rank = rank;
   p.tp = tp;
   p.slot_bytes = slot_bytes;
-  p.state = static_cast<uint32_t*>(state);
+  p.state = static_cast<uint64_t*>(state);
   p.status = ctx->status_dev;
   p.limit_ns = wait_limit_ns();
   // 4 KiB of the message per block and pass

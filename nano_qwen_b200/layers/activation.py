@@ -14,7 +14,8 @@ class SiluAndMul(nn.Module):
 
     With ``emit_fp8=True`` (default) a CUDA bf16 input yields a :class:`QuantizedActivation` — the bf16 result of the
     reference, quantised per token and 128-wide group by the same kernel pass — which ``RowParallelLinear`` (down_proj)
-    consumes without a quantiser launch.  ``emit_fp8=False`` is the reference's eager arithmetic in torch.
+    consumes without a quantiser launch; any other input raises (the FP8 path has no CPU or other-dtype fallback).
+    ``emit_fp8=False`` is not part of the FP8 path: it is the reference's eager arithmetic in torch.
     """
 
     def __init__(self, emit_fp8: bool = True):
@@ -22,9 +23,12 @@ class SiluAndMul(nn.Module):
         self.emit_fp8 = emit_fp8
 
     def forward(self, x: torch.Tensor):
-        if not (self.emit_fp8 and x.is_cuda and x.dtype == torch.bfloat16):
+        if not self.emit_fp8:
             gate, up = x.chunk(2, -1)
             return F.silu(gate) * up
+        if not x.is_cuda or x.dtype != torch.bfloat16:
+            raise RuntimeError(f"SiluAndMul(emit_fp8=True) needs a CUDA bfloat16 tensor, got {x.device.type} {x.dtype}: "
+                               "there is no CPU fallback (construct it with emit_fp8=False for the eager op)")
         inter = x.shape[-1] // 2
         xq, sx = ops.silu_mul_quant(x.reshape(-1, x.shape[-1]))
         return QuantizedActivation(xq, sx, (*x.shape[:-1], inter))

@@ -111,3 +111,14 @@ def get_reducer() -> P2PRowReducer | None:
         return None                        # set-up allocates and talks to the peers: not during a capture
     _reducer = P2PRowReducer(max_message_bytes(tp))
     return _reducer
+
+
+def init() -> bool:
+    """Creates the peer-memory reducer now instead of inside the first row-parallel ``forward``.
+
+    A collective call (every rank of the default group must make it) that allocates and exchanges handles, so it
+    must not happen during CUDA-graph capture: a model runner calls it once after ``init_process_group`` and before
+    ``capture_cudagraph``; otherwise a first forward that happens under capture keeps NCCL for that graph.
+    Returns whether the peer-memory path is in use.
+    """
+    return get_reducer() is not None

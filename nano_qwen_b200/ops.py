@@ -50,6 +50,23 @@ def launch_count() -> int:
     return int(_cabi.lib().nq_launch_count())
 
 
+def check_device_status(reset: bool = True) -> None:
+    """Raises :class:`_cabi.NqError` if a bounded device-side wait ran out since the last check.
+
+    The kernels never trap: a wait that expires (a peer of the row-parallel sum that never arrived, a pipeline
+    barrier that was never signalled) lets its kernel finish with an incomplete result and records the fact in a
+    status block.  Call this where the host synchronises anyway (after a step's outputs were read); it does not
+    synchronise itself.  ``reset`` clears the block so that the next check reports only new events.
+    """
+    st = _cabi.device_status()
+    if st["code"] != 0:
+        if reset:
+            _cabi.device_status(reset=True)
+        raise _cabi.NqError(st["code"], "device status",
+                            f"{_cabi.lib().nq_status_string(st['code']).decode()}: wait site {st['where']}, "
+                            f"block {st['block']}, aux {st['aux']}")
+
+
 def act_quant(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """Dynamic per-token 1x128 quantiser.
 

@@ -11,6 +11,14 @@ if ROOT not in sys.path:
 GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 
+def free_port() -> int:
+    """A TCP port that is free right now (the machine is shared: no fixed rendezvous ports)."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
 
@@ -30,7 +38,7 @@ def single_rank_group():
     import torch.distributed as dist
     if not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29731")
+        os.environ.setdefault("MASTER_PORT", str(free_port()))
         dist.init_process_group("gloo", rank=0, world_size=1)
     yield
     # left initialised for the rest of the session; destroyed at interpreter exit

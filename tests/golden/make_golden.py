@@ -19,6 +19,13 @@ What it records
     through their loaders and run through their ``forward`` on CPU in fp32
     (row-parallel layers all-reduced over gloo).  Outputs are stored as bf16
     bit patterns, inputs as sha256 digests.
+``checkpoint_digests.json``, ``checkpoint_probe_tp{1,2}.npz``
+    The synthetic tiny Qwen3-dense-shaped checkpoint of ``oracle/synth_checkpoint.py`` (dequantised variant) loaded
+    by the reference's own ``load_model`` (``nano_qwen/utils/loader.py:12-28``) into a tree of the reference's
+    ``QKVParallelLinear`` / ``MergedColumnParallelLinear`` / ``RowParallelLinear`` / ``VocabParallelEmbedding`` /
+    ``RMSNorm`` under real gloo ranks, tp in {1,2,4,8}: sha256 of every rank's parameters (as fp32), and for tp in
+    {1,2} the outputs of every packed linear on seeded probe activations (quantised and dequantised by the oracle
+    recipe first).  The script also checks that ``oracle/ref_loader.py`` places exactly what ``load_model`` places.
 ``fused_ops.npz``
     The reference's ``SiluAndMul``, ``RMSNorm`` and ``GemmaRMSNorm`` (``layers/activation.py``, ``layers/layernorm.py``)
     run on CPU in bf16 with ``torch.compile`` switched off (``TORCHDYNAMO_DISABLE=1``), on seeded inputs of the
@@ -40,7 +47,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 
-from oracle import fp8_spec, synth  # noqa: E402
+from oracle import fp8_spec, ref_loader, synth, synth_checkpoint  # noqa: E402
 
 SHARD_CASES = {
     # kind: constructor args for the small index-coded case
@@ -171,6 +178,64 @@ def worker(rank: int, tp: int, port: int, ref_src: str, outdir: str):
     dist.destroy_process_group()
 
 
+def param_digests(model) -> dict:
+    return {name: synth.digest(p.data.float().contiguous().view(torch.uint8)) for name, p in model.named_parameters()}
+
+
+def checkpoint_worker(rank: int, tp: int, port: int, ref_src: str, ckpt: str, outdir: str):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=tp)
+    sys.path.insert(0, ref_src)
+    torch.set_default_dtype(torch.float32)
+    from nano_qwen.layers import linear as ref
+    from nano_qwen.layers.embed_head import VocabParallelEmbedding
+    from nano_qwen.layers.layernorm import RMSNorm
+    from nano_qwen.utils.loader import load_model
+
+    def tree():
+        return synth_checkpoint.build_tree(ref, rank, tp, embed_cls=VocabParallelEmbedding,
+                                           norm_cls=lambda n: RMSNorm(n, eps=1e-6))
+    model = tree()
+    load_model(model, ckpt)                                   # the reference's own loop
+    digests = param_digests(model)
+    again = tree()
+    ref_loader.load_model(again, ckpt)                        # the restatement must place the same bytes
+    assert param_digests(again) == digests, "oracle/ref_loader.py disagrees with nano_qwen.utils.loader.load_model"
+    with open(os.path.join(outdir, f"ckpt_tp{tp}_r{rank}.json"), "w") as f:
+        json.dump(digests, f)
+    if tp in (1, 2):
+        res = {}
+        for name, x in synth_checkpoint.probe_inputs().items():
+            mod = model.model.get_submodule(name)
+            xq, sx = fp8_spec.quantize_act_group128(x)
+            xd = fp8_spec.dequantize_act(xq, sx)
+            if isinstance(mod, ref.RowParallelLinear):
+                ks = xd.shape[1] // tp
+                xd = xd[:, rank * ks:(rank + 1) * ks].contiguous()
+            res[f"{name}_r{rank}"] = mod(xd).detach().to(torch.bfloat16).view(torch.int16).numpy()
+        np.savez(os.path.join(outdir, f"ckpt_probe_tp{tp}_r{rank}.npz"), **res)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def checkpoint_case(ref_src: str, port: int) -> None:
+    tmp = tempfile.mkdtemp()
+    ckpt = synth_checkpoint.write(os.path.join(tmp, "dequantised"), seed=0, quantised=False)
+    digests = {}
+    for i, tp in enumerate((1, 2, 4, 8)):
+        mp.spawn(checkpoint_worker, args=(tp, port + i, ref_src, ckpt, tmp), nprocs=tp, join=True)
+        digests[f"tp{tp}"] = [json.load(open(os.path.join(tmp, f"ckpt_tp{tp}_r{r}.json"))) for r in range(tp)]
+        if tp in (1, 2):
+            merged = {}
+            for r in range(tp):
+                with np.load(os.path.join(tmp, f"ckpt_probe_tp{tp}_r{r}.npz")) as z:
+                    merged.update({k: z[k] for k in z.files})
+            np.savez_compressed(os.path.join(HERE, f"checkpoint_probe_tp{tp}.npz"), **merged)
+    with open(os.path.join(HERE, "checkpoint_digests.json"), "w") as f:
+        json.dump(digests, f, separators=(",", ":"))
+
+
 def fused_ops(ref_src: str) -> None:
     """Runs in a child interpreter: the compiler switch has to be set before torch is imported."""
     import subprocess
@@ -204,9 +269,13 @@ np.savez_compressed(sys.argv[2], **out)
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    ref_src = os.path.join(ref_root, "src")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/nano_qwen [--only-checkpoint]")
+    ref_src = os.path.join(sys.argv[1], "src")
     assert os.path.isdir(ref_src), ref_src
+    checkpoint_case(ref_src, 29631)
+    if "--only-checkpoint" in sys.argv:
+        return
     fused_ops(ref_src)
     tmp = tempfile.mkdtemp()
     sharding = {"cases": SHARD_CASES}

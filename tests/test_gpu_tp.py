@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from conftest import GOLDEN, ROOT
+from conftest import GOLDEN, ROOT, free_port
 
 pytestmark = pytest.mark.gpu
 
@@ -165,7 +165,7 @@ def test_two_gpu_layers_match_the_reference_two_rank_run(tmp_path, built_library
         pytest.skip("needs 2 GPUs")
     from oracle import fp8_spec as S
     out = str(tmp_path / "r{rank}.npz")
-    mp.spawn(_worker, args=(2, 29671, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, free_port(), out), nprocs=2, join=True)
     with np.load(os.path.join(GOLDEN, "linear_tp2.npz")) as gold:
         got = [np.load(out.format(rank=r)) for r in range(2)]
         for r in range(2):

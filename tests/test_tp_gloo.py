@@ -16,7 +16,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from conftest import GOLDEN, ROOT
+from conftest import GOLDEN, ROOT, free_port
 
 
 def _oracle_linear(self, x, bias):
@@ -76,7 +76,7 @@ def _worker(rank, world, port, out_path):
 def test_two_rank_layers_match_the_reference_two_rank_run(tmp_path):
     from oracle import fp8_spec as S
     out = str(tmp_path / "r{rank}.npz")
-    mp.spawn(_worker, args=(2, 29655, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, free_port(), out), nprocs=2, join=True)
     with np.load(os.path.join(GOLDEN, "linear_tp2.npz")) as gold:
         got = [np.load(out.format(rank=r)) for r in range(2)]
         for r in range(2):
@@ -92,3 +92,39 @@ def test_two_rank_layers_match_the_reference_two_rank_run(tmp_path):
         # all-reduce: both ranks hold the same reduced tensor
         for name in ("o_proj", "down"):
             assert np.array_equal(got[0][name], got[1][name])
+
+
+def _absent_rank_worker(rank, world, port, out_path):
+    """Rank 1 never reaches the row-parallel forward; rank 0 must learn of it on the host and carry on."""
+    import datetime
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    from nano_qwen_b200.layers import linear as L
+    L.LinearBase._linear = _oracle_linear
+    row = L.RowParallelLinear(256, 128)
+    row.weight.weight_loader(row.weight, torch.zeros(128, 256).to(torch.float8_e4m3fn))
+    dist.barrier()                                   # both ranks are up: the failure happens between steps
+    if rank == 1:
+        time.sleep(8)                                # stays away for longer than the group's time limit, then leaves
+        os._exit(0)
+    t0 = time.perf_counter()
+    try:
+        row(torch.ones(4, 128))
+        verdict = "no error"
+    except RuntimeError as e:                        # the collective's time limit ends the wait with an error
+        verdict = "timeout reported" if time.perf_counter() - t0 < 7.5 else "late: " + str(e)[:80]
+    with open(out_path, "w") as f:
+        f.write(verdict)
+    os._exit(0)                                      # the group is broken: leave without the collective teardown
+
+
+@pytest.mark.timeout(120)
+def test_a_rank_that_never_arrives_is_reported_on_the_host(tmp_path):
+    """Failure detection without a GPU fault: the peer is lost between steps, the survivor's next all-reduce ends
+    with an error inside the process group's time limit instead of waiting for ever."""
+    out = str(tmp_path / "verdict.txt")
+    mp.spawn(_absent_rank_worker, args=(2, free_port(), out), nprocs=2, join=True)
+    assert open(out).read() == "timeout reported"

@@ -3,7 +3,7 @@
 ``nq_fp8_linear_noalloc`` serves hosts that cannot give the library scratch memory: it keeps the quantised
 activations in a fixed array inside the library image.  Here it is called twice in a row through the C ABI,
 with different inputs, and each result is compared with ``nq_fp8_linear`` (caller-allocated scratch) on the
-same inputs.  The second call checks that nothing left in the shared array by the first one leaks into it.
+same inputs and with the CPU oracle.  The second call checks that nothing left in the shared array by the first one leaks into it.
 """
 import pytest
 import torch
@@ -50,6 +50,10 @@ def test_noalloc_entry_matches_the_ordinary_one_twice_in_a_row(lib):
         assert not torch.isnan(y.float()).any()
         assert S.max_rel_err(y.cpu(), expect.cpu()) <= PARITY
         assert torch.equal(y, expect)                        # same kernels, same scratch contents: same bits
+        # and against the CPU oracle (dequantise both operands, fp32 matmul, bf16 out), not only against the sibling entry
+        xq_ref, sx_ref = S.quantize_act_group128(x.cpu())
+        ref = S.linear_dequant_matmul(xq_ref, sx_ref, wq.cpu(), sw.cpu(), bias.cpu() if use_bias else None)
+        assert S.max_rel_err(y.cpu(), ref) <= PARITY
 
 
 def test_noalloc_entry_refuses_sizes_beyond_its_array(lib):
