@@ -1,4 +1,10 @@
-"""Tensor-parallel layers on 2 GPUs with NCCL against the reference's own 2-rank run (skipped on 1-GPU boxes)."""
+"""Tensor-parallel layers on 2, 4 and 8 GPUs with NCCL (each case skipped where the box has fewer GPUs).
+
+World size 2 is checked against the reference's own 2-rank run (``tests/golden/linear_tp2.npz``,
+``checkpoint_probe_tp2.npz``); 4 and 8 against the oracle's restatement of the sharded forward
+(``oracle/ref_linear.py``), which the CPU tests pin to the reference at 1 and 2 ranks.  Every world size also checks
+the three peer-memory reductions against NCCL's all-reduce and that all ranks end with the same bits.
+"""
 import os
 import sys
 
@@ -13,7 +19,7 @@ from conftest import GOLDEN, ROOT, free_port
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, out_path):
+def _worker(rank, world, port, out_path, ckpt_dir):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -80,7 +86,7 @@ def _worker(rank, world, port, out_path):
         torch.cuda.synchronize()
         # same sums up to fp32 summation order (the chunked launches may split K differently)
         err = (piped.float() - single.float()).abs().max() / single.float().abs().max()
-        res["pipelined_close_to_single"] = (err <= 8e-3).to(torch.int16).reshape(1)
+        res["pipelined_close_to_single"] = (err <= (8e-3 if world == 2 else 2e-2)).to(torch.int16).reshape(1)
         # ---- Qwen3-32B-shaped row layer (down_proj, K = 25600 split over the ranks) against the unsharded product ----
         K32, N32 = synth.STACKS["qwen3-32b"]["down"]
         g32 = torch.Generator(device="cuda").manual_seed(4242)            # same seed on every rank: same tensors
@@ -102,7 +108,7 @@ def _worker(rank, world, port, out_path):
             part = row32(x32[:, rank * ks:(rank + 1) * ks].contiguous())   # this rank's K-slice + the sum over ranks
             torch.cuda.synchronize()
             err = float((part.float() - full.float()).abs().max() / full.float().abs().max())
-            ok32 &= int(err <= 8e-3)                                       # partials are rounded to bf16 before the sum
+            ok32 &= int(err <= (8e-3 if world == 2 else 2e-2))                                       # partials are rounded to bf16 before the sum
         res["row_32b_matches_unsharded"] = torch.tensor([ok32], dtype=torch.int16)
         del row32, wq32, sw32
         # ---- the peer-memory sum (decode-sized outputs) against NCCL's all-reduce ----
@@ -117,10 +123,14 @@ def _worker(rank, world, port, out_path):
             t = torch.randn(n, generator=gen, device="cuda").to(torch.bfloat16)
             want = t.clone()
             dist.all_reduce(want)
-            assert reducer.fits(t), n
+            if not reducer.fits(t):                       # the size limit of the one-shot exchange shrinks with the group
+                assert n * 2 > p2p_reduce.max_message_bytes(world)
+                continue
             got_t = reducer.reduce_(t.clone())
             worst = max(worst, float((got_t.float() - want.float()).abs().max() / want.float().abs().max()))
-        res["p2p_vs_nccl_ok"] = torch.tensor([1 if worst <= 2 ** -7 else 0], dtype=torch.int16)
+        # NCCL rounds partial sums to bf16 along its ring, the kernel adds in fp32: one bf16 ulp at 2 ranks, two beyond
+        tol = 2 ** -7 if world == 2 else 2 ** -6
+        res["p2p_vs_nccl_ok"] = torch.tensor([1 if worst <= tol else 0], dtype=torch.int16)
         # a graph that holds nothing but one row layer, replayed with fresh inputs: the call counter lives on the device
         row = rows["o_proj"]
         xs = torch.zeros(16, shapes["o_proj"][0] // world, dtype=torch.bfloat16, device="cuda")
@@ -141,10 +151,45 @@ def _worker(rank, world, port, out_path):
             row.p2p_reduce = True
             torch.cuda.synchronize()
             err = float((yg.float() - ref.float()).abs().max() / ref.float().abs().max())
-            replay_ok &= int(err <= 2 ** -7)
+            replay_ok &= int(err <= tol)
         res["p2p_graph_replays_ok"] = torch.tensor([replay_ok], dtype=torch.int16)
         res["p2p_result_for_rank_equality"] = yg.clone().reshape(-1)
         del g, yg
+        # ---- prefill-sized sums: in-switch (multimem) and pull-based peer-memory kernels against NCCL ----
+        from nano_qwen_b200.layers import mc_reduce
+        big_ok, big_same = 1, []
+        mc = mc_reduce.get_reducer()
+        if mc is not None:
+            for rows_, cols_ in ((8, 4096), (2048, 4096), (1000, 5120)):
+                src = torch.randn(rows_, cols_, generator=gen, device="cuda").to(torch.bfloat16)
+                want = src.clone()
+                dist.all_reduce(want)
+                part = mc.partial(rows_, cols_)
+                part.copy_(src)
+                got_mc = mc.reduce_(part).clone()
+                part.copy_(src)
+                got_pull = mc.reduce_pull(part)
+                torch.cuda.synchronize()
+                for got_t in (got_mc, got_pull):
+                    e = float((got_t.float() - want.float()).abs().max() / want.float().abs().max())
+                    big_ok &= int(e <= 2 ** -6)           # NCCL rounds partial sums to bf16 along its ring; these add in fp32
+                    big_same.append(got_t.reshape(-1)[:4096].clone())
+        res["big_reduce_vs_nccl_ok"] = torch.tensor([big_ok], dtype=torch.int16)
+        res["big_reduce_for_rank_equality"] = torch.cat(big_same) if big_same else torch.zeros(8, dtype=torch.bfloat16)
+        # ---- FP8 checkpoint files -> loader loop -> this rank's shards -> forward on probe activations ----
+        from oracle import ref_loader, synth_checkpoint as CK
+        torch.set_default_device("cuda")
+        torch.set_default_dtype(torch.bfloat16)
+        tree = CK.build_tree(L, rank, world)
+        torch.set_default_device("cpu")
+        torch.set_default_dtype(torch.float32)
+        ref_loader.load_model(tree, ckpt_dir)
+        for pname, px in CK.probe_inputs().items():
+            mod = tree.model.get_submodule(pname)
+            if isinstance(mod, L.RowParallelLinear):
+                ks = px.shape[1] // world
+                px = px[:, rank * ks:(rank + 1) * ks].contiguous()
+            res["ckpt_" + pname] = mod(px.cuda())
         torch.cuda.synchronize()
         res["device_status"] = torch.tensor([_cabi.device_status()["code"]], dtype=torch.int16)
         np.savez(out_path.format(rank=rank), **{k: v.cpu().view(torch.int16).numpy() for k, v in res.items()})
@@ -159,27 +204,69 @@ def _worker(rank, world, port, out_path):
     os._exit(0)
 
 
-@pytest.mark.timeout(300)
-def test_two_gpu_layers_match_the_reference_two_rank_run(tmp_path, built_library):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    from oracle import fp8_spec as S
+def _oracle_outputs(world):
+    """What every rank of a ``world``-rank run must hold for the 0.6B-shaped stack (oracle restatement of the sharded
+    forward, fp32 on the CPU, dequantised operands)."""
+    from oracle import fp8_spec as S, ref_linear as R, synth
+    weights, acts = synth.make_stack("qwen3-0.6b", 16, seed=0)
+    shapes = synth.STACKS["qwen3-0.6b"]
+    out = {}
+    dq = {}
+    for name in synth.LAYER_ORDER:
+        wq, sw = S.quantize_weight_block128(weights[name])
+        xq, sx = S.quantize_act_group128(acts[name])
+        dq[name] = (S.dequantize_act(xq, sx), S.dequantize_weight(wq, sw))
+    N = shapes["qkv"][1]
+    nq = N - 2048
+    for r in range(world):
+        x, w = dq["qkv"]
+        out[("qkv", r)] = R.column_forward(x, R.qkv_param(w[:nq], w[nq:nq + 1024], w[nq + 1024:], r, world)).to(torch.bfloat16)
+        x, w = dq["gate_up"]
+        half = w.shape[0] // 2
+        out[("gate_up", r)] = R.column_forward(x, R.merged_column_param([w[:half], w[half:]], r, world)).to(torch.bfloat16)
+    for name in ("o_proj", "down"):
+        x, w = dq[name]
+        out[(name, None)] = R.row_forward(x, w, None, world).to(torch.bfloat16)
+    return out
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_layers_on_real_ranks(tmp_path, built_library, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from oracle import fp8_spec as S, synth_checkpoint as CK
     out = str(tmp_path / "r{rank}.npz")
-    mp.spawn(_worker, args=(2, free_port(), out), nprocs=2, join=True)
-    with np.load(os.path.join(GOLDEN, "linear_tp2.npz")) as gold:
-        got = [np.load(out.format(rank=r)) for r in range(2)]
-        for r in range(2):
-            for name in ("qkv", "gate_up", "o_proj", "down"):
-                mine = torch.from_numpy(got[r][name]).view(torch.bfloat16)
-                ref = torch.from_numpy(gold[f"y_{name}_r{r}"]).view(torch.bfloat16)
-                assert S.max_rel_err(mine, ref) <= 2e-2, (name, r)
-            for name in ("o_proj", "down"):
-                assert np.array_equal(got[r][name], got[r][name + "_graph"]), name     # graph replay == eager
-            assert int(got[r]["pipelined_close_to_single"][0]) == 1
-            assert int(got[r]["row_32b_matches_unsharded"][0]) == 1
-            assert int(got[r]["p2p_vs_nccl_ok"][0]) == 1
-            assert int(got[r]["p2p_graph_replays_ok"][0]) == 1
-            assert int(got[r]["device_status"][0]) == 0
-        assert np.array_equal(got[0]["p2p_result_for_rank_equality"], got[1]["p2p_result_for_rank_equality"])
+    ckpt = CK.write(str(tmp_path / "ckpt"), seed=0, quantised=True)
+    mp.spawn(_worker, args=(world, free_port(), out, ckpt), nprocs=world, join=True)
+    got = [np.load(out.format(rank=r)) for r in range(world)]
+    bf16 = lambda a: torch.from_numpy(a).view(torch.bfloat16)
+    want = _oracle_outputs(world)
+    for r in range(world):
+        for name in ("qkv", "gate_up"):
+            assert S.max_rel_err(bf16(got[r][name]), want[(name, r)]) <= 2e-2, (name, r)
         for name in ("o_proj", "down"):
-            assert np.array_equal(got[0][name], got[1][name])                          # both ranks hold the sum
+            assert S.max_rel_err(bf16(got[r][name]), want[(name, None)]) <= 2e-2, (name, r)
+            assert np.array_equal(got[r][name], got[r][name + "_graph"]), name     # graph replay == eager
+            assert np.array_equal(got[0][name], got[r][name])                      # every rank holds the same sum
+        assert int(got[r]["pipelined_close_to_single"][0]) == 1
+        assert int(got[r]["row_32b_matches_unsharded"][0]) == 1
+        assert int(got[r]["p2p_vs_nccl_ok"][0]) == 1
+        assert int(got[r]["p2p_graph_replays_ok"][0]) == 1
+        assert int(got[r]["big_reduce_vs_nccl_ok"][0]) == 1
+        assert int(got[r]["device_status"][0]) == 0
+        assert np.array_equal(got[0]["p2p_result_for_rank_equality"], got[r]["p2p_result_for_rank_equality"])
+        assert np.array_equal(got[0]["big_reduce_for_rank_equality"], got[r]["big_reduce_for_rank_equality"])
+    if world == 2:                       # the reference's own two-rank run
+        with np.load(os.path.join(GOLDEN, "linear_tp2.npz")) as gold, \
+                np.load(os.path.join(GOLDEN, "checkpoint_probe_tp2.npz")) as gold_ck:
+            for r in range(2):
+                for name in ("qkv", "gate_up", "o_proj", "down"):
+                    assert S.max_rel_err(bf16(got[r][name]), bf16(gold[f"y_{name}_r{r}"])) <= 2e-2, (name, r)
+                for pname in CK.probe_inputs():
+                    assert S.max_rel_err(bf16(got[r]["ckpt_" + pname]), bf16(gold_ck[f"{pname}_r{r}"])) <= 2e-2, (pname, r)
+    else:                                # the loaded checkpoint's row layers agree across ranks
+        for pname in CK.probe_inputs():
+            if pname.endswith(("o_proj", "down_proj")):
+                for r in range(1, world):
+                    assert np.array_equal(got[0]["ckpt_" + pname], got[r]["ckpt_" + pname]), pname
