@@ -63,7 +63,6 @@ extern "C" {
 #define NQ_ALGO_TOKEN_LANE_192 4 /* (NQ_ALGO_TOKEN_LANE picks the width itself)                        */
 #define NQ_ALGO_TOKEN_LANE_256 5
 #define NQ_ALGO_TOKEN_PAIR 6 /* token-lane on CTA pairs: one 256x256 tile per two SMs (tcgen05 cta_group::2) */
-#define NQ_ALGO_TOKEN_PAIR_128 7 /* the same with 256x128 tiles (four TMEM accumulators in flight) */
 #define NQ_ALGO_WEIGHT_LANE_FUSED 8 /* nq_fp8_linear only: weight-lane with the activation quantiser inside the GEMM
                                        kernel (M <= NQ_FUSED_MAX_TOKENS, K and ldx multiples of 8, x 16-byte aligned) */
 #define NQ_FUSED_MAX_TOKENS 32  /* most tokens NQ_ALGO_WEIGHT_LANE_FUSED accepts */

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libnq_fp8.s
 NQ_OK = 0
 ALGO_AUTO, ALGO_TOKEN_LANE, ALGO_WEIGHT_LANE = 0, 1, 2
 ALGO_TOKEN_LANE_128, ALGO_TOKEN_LANE_192, ALGO_TOKEN_LANE_256 = 3, 4, 5
-ALGO_TOKEN_PAIR, ALGO_TOKEN_PAIR_128 = 6, 7
+ALGO_TOKEN_PAIR = 6
 ALGO_WEIGHT_LANE_FUSED = 8
 FUSED_MAX_TOKENS, FUSED_AUTO_TOKENS = 32, 8      # NQ_FUSED_MAX_TOKENS, NQ_FUSED_AUTO_TOKENS
 

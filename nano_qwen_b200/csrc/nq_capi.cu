@@ -1,6 +1,7 @@
 // extern "C" entry points of libnq_fp8.so and the per-device set-up behind them.
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -140,7 +141,6 @@ int gemm_dispatch(const GemmArgs& a, int algo) {
   if (algo == NQ_ALGO_TOKEN_LANE_256) return launch_gemm_token_lane(a, ctx, 256);
   if (algo == NQ_ALGO_WEIGHT_LANE) return launch_gemm_weight_lane(a, ctx);
   if (algo == NQ_ALGO_TOKEN_PAIR) return launch_gemm_token_pair(a, ctx, 256);
-  if (algo == NQ_ALGO_TOKEN_PAIR_128) return launch_gemm_token_pair(a, ctx, 128);
   return NQ_ERR_BAD_ARGUMENT;
 }
 

@@ -539,13 +539,18 @@ token_lane_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 // =========================================================================== //
 //                        token-lane kernel, CTA pairs                          //
 // =========================================================================== //
-// Same computation as token_lane_kernel<256>, but two CTAs of a cluster share one 256 x 256 output tile:
+// Same computation as token_lane_kernel<256>, but two CTAs of a cluster share one 256 x BN output tile:
 // each owns 128 token rows (its own A tile and TMEM accumulators) and loads only HALF of the weight
-// rows of a K-tile; one tcgen05.mma.cta_group::2 (issued by the leader CTA) multiplies 256 x 256 x 32 on
+// rows of a K-tile; one tcgen05.mma.cta_group::2 (issued by the leader CTA) multiplies 256 x BN x 32 on
 // both SMs, reading the other half of B from the peer's shared memory.  Operand traffic per SM drops from
-// 48 KB to 32 KB per K-tile and the ring holds 6 stages.  No multicast is used: both CTAs issue plain TMA
-// loads whose completion is counted on the leader's barrier, and UMMA completion is signalled to each
-// CTA's barriers by separate commits.
+// 48 KB to 32 KB per K-tile (BN = 256) - the L2 -> SM path, not the tensor pipe, is what bounds the
+// single-CTA kernel - and the ring holds 6 stages.  Everything else is the single-CTA kernel's design: two
+// issuing threads (in the leader) taking alternate K-tiles, a scale-loader warp per CTA, eight epilogue
+// warps per CTA with the 64 / 216 register split and TMA stores from shared memory.
+// No multicast is used anywhere: both CTAs issue plain TMA loads whose completion bytes are counted on the
+// leader's barrier, UMMA completion is signalled to each CTA's barriers by separate commits, and the
+// follower's epilogue warps hand accumulators back with remote mbarrier arrivals (plain arrivals: an arrival with
+// cluster-scope release semantics measured twice as slow for the whole kernel, 1000 against 2000 TFLOP/s).
 template <int BN>
 struct TokenPair {
   static constexpr int kHalfRows = BN / 2;                      // weight rows of a K-tile that one CTA loads
@@ -554,17 +559,19 @@ struct TokenPair {
   static constexpr int kEpiWarps = 8;
   static constexpr int kFirstEpiWarp = 4;
   static constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
-  static constexpr int kCols = BN / 2;
+  static constexpr int kCols = BN / 2;                          // accumulator columns per epilogue thread
   static constexpr int kNumAcc = 512 / BN;                      // 2 x 256 or 4 x 128 TMEM columns
   static constexpr int kTmemCols = 512;
   static constexpr int kScaleBytes = kNumAcc * 2 * 128 * 4;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + 1024;
+  static constexpr int kStoreBytes = kEpiWarps * 2048;          // per epilogue warp two 32 x 16 bf16 staging tiles
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kStoreBytes + 1024;
   static constexpr int kGroupM = 8;                             // pair-tiles (256 rows) per rasterisation group
   static constexpr int kScalePrefetch = 4;
-  static constexpr int kRegsLow = 56;
-  static constexpr int kRegsHigh = 224;
+  static constexpr int kRegsLow = 64;
+  static constexpr int kRegsHigh = 216;
   static constexpr int kRegsNeeded = kRegsLow + (kThreads / 128 - 1) * kRegsHigh;
   static_assert(kRegsNeeded <= (65536 / kThreads / 8 * 8) * (kThreads / 128), "setmaxnreg split exceeds the register pool");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
 struct __align__(8) PairBars {
@@ -574,6 +581,7 @@ struct __align__(8) PairBars {
   uint64_t tmem_empty[4];    // used in the leader: all 16 epilogue warps of the pair have drained
   uint64_t slot_free[4];     // per CTA: the 8 local epilogue warps have read scale slot and accumulator
   uint64_t teardown;
+  uint64_t teardown2;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -592,12 +600,13 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int num_m2, int num_n
 template <int BN>
 __global__ void __launch_bounds__(TokenPair<BN>::kThreads, 1)
 token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                  const TokenLaneParams p) {
+                  const __grid_constant__ CUtensorMap tm_y, const TokenLaneParams p) {
   using C = TokenPair<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align_1024(smem_raw);
   float* scale_ring = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);   // [kNumAcc][2][128]
-  PairBars* bars = reinterpret_cast<PairBars*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes);
+  uint8_t* store_ring = smem + C::kStages * C::kStageBytes + C::kScaleBytes;            // [epilogue warp][2][32 rows x 32 B]
+  PairBars* bars = reinterpret_cast<PairBars*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes + C::kStoreBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();              // 0 = leader (issues the UMMAs)
@@ -612,10 +621,12 @@ token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       mbar_init(&bars->slot_free[b], C::kEpiWarps);
     }
     mbar_init(&bars->teardown, 1);
+    mbar_init(&bars->teardown2, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_w);
+    if (p.y_tma) tma_prefetch_desc(&tm_y);
   }
   if (warp == 1) { tmem_alloc_pair(&bars->tmem_base, C::kTmemCols); tmem_relinquish_pair(); }
   tc_fence_before_sync();
@@ -657,39 +668,44 @@ token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
       }
     }
-   } else if (warp == 1) {
-    // ------------------------------ MMA issuer (leader only) ------------------------------
+   } else if (warp == 1 || warp == 3) {
+    // ------------------------------ MMA issuers (leader only) ------------------------------
+    // Two issuing threads take alternate K-tiles (different stages, different accumulators), so that the barrier
+    // waits and commits of one overlap the UMMAs of the other.
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(256, BN);
+      const uint32_t mine = (warp == 1) ? 0u : 1u;
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
         for (int kt = 0; kt < KT; ++kt, ++it) {
+          if ((it & 1u) != mine) continue;
           const int b = it % C::kNumAcc;
           const uint32_t aph = (it / C::kNumAcc) & 1;
-          if (!mbar_wait_cluster(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
           const int s = it % C::kStages;
           const uint32_t ph = (it / C::kStages) & 1;
-          if (!mbar_wait_cluster(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
-          tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
           const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
           const uint64_t b_desc = umma_smem_desc_sw128(a_addr + kLaneTileBytes);
           const uint32_t d = tmem_base + b * BN;
+          if (!mbar_wait(&bars->tmem_empty[b], aph ^ 1, ac, kSiteMmaTmemEmpty, kt)) { ok = false; break; }
+          if (!mbar_wait(&bars->full[s], ph, ac, kSiteMmaFull, kt)) { ok = false; break; }
+          tc_fence_after_sync();
 #pragma unroll
           for (int k = 0; k < kTileK / 32; ++k)
             umma_f8_pair(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
           // completion goes to this stage's "empty" and this accumulator's "full" barrier of BOTH CTAs
-          umma_commit_pair(smem_u32(&bars->empty[s]));
-          umma_commit_pair(mapa_shared(smem_u32(&bars->empty[s]), 1));
           umma_commit_pair(smem_u32(&bars->tmem_full[b]));
           umma_commit_pair(mapa_shared(smem_u32(&bars->tmem_full[b]), 1));
+          umma_commit_pair(smem_u32(&bars->empty[s]));
+          umma_commit_pair(mapa_shared(smem_u32(&bars->empty[s]), 1));
         }
       }
-      if (!ok) {
-        umma_commit_pair(smem_u32(&bars->teardown));
+      if (!ok) {   // let MMAs already issued finish before TMEM is freed
+        uint64_t* td = (warp == 1) ? &bars->teardown : &bars->teardown2;
+        umma_commit_pair(smem_u32(td));
         const long long t0 = clock64();
-        while (!mbar_try_wait(&bars->teardown, 0) && clock64() - t0 < 40000000ll) {}
+        while (!mbar_try_wait(td, 0) && clock64() - t0 < 40000000ll) {}
       }
     }
    } else if (warp == 2) {
@@ -763,20 +779,22 @@ token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const int q = warp & 3;
     const int h = (warp - C::kFirstEpiWarp) >> 2;
     const int row = q * 32 + lane;
+    const uint32_t leader_tmem_empty0 = mapa_shared(smem_u32(&bars->tmem_empty[0]), 0);
     float acc[C::kCols];
     uint32_t it = 0;
     bool ok = true;
     for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
       int m2, n_t;
       pair_tile_coords(tile, num_m2, num_n, m2, n_t);
-      const int m = m2 * 256 + static_cast<int>(rank) * 128 + row;
+      const int m0 = m2 * 256 + static_cast<int>(rank) * 128;
+      const int m = m0 + row;
       const int n_base = n_t * BN + h * C::kCols;
 #pragma unroll
       for (int i = 0; i < C::kCols; ++i) acc[i] = 0.0f;
       for (int kt = 0; kt < KT; ++kt, ++it) {
         const int b = it % C::kNumAcc;
         const uint32_t aph = (it / C::kNumAcc) & 1;
-        if (!mbar_wait_cluster(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt)) { ok = false; break; }
+        if (!mbar_wait(&bars->tmem_full[b], aph, ac, kSiteEpiTmemFull, kt)) { ok = false; break; }
         tc_fence_after_sync();
         const float s = scale_ring[(b * 2 + h) * 128 + row];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * BN + h * C::kCols;
@@ -796,14 +814,47 @@ token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
+          mbar_arrive_remote(leader_tmem_empty0 + b * 8);                              // the leader's UMMA issuers
           mbar_arrive(&bars->slot_free[b]);                                            // local scale loader
-          mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[b]), 0));          // the leader's UMMA issuer
         }
         promote32(acc + C::kCols - 64, ra, s);
         promote32(acc + C::kCols - 32, rb, s);
       }
       if (!ok) break;
-      if (m < p.M) {
+      if (p.y_tma) {
+        // through shared memory and TMA, as in the single-CTA kernel
+        uint8_t* stg = store_ring + (warp - C::kFirstEpiWarp) * 2048;
+#pragma unroll
+        for (int j = 0; j < C::kCols; j += 16) {
+          const int n = n_base + j;
+          if (n >= p.N) break;                                  // warp-uniform
+          uint8_t* buf = stg + ((j >> 4) & 1) * 1024;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = acc[j + i];
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (n + i < p.N) v[i] += bf16_to_float(p.bias + n + i);
+          }
+          uint4 o0, o1;
+          o0.x = pack_bf16x2(v[0], v[1]);   o0.y = pack_bf16x2(v[2], v[3]);
+          o0.z = pack_bf16x2(v[4], v[5]);   o0.w = pack_bf16x2(v[6], v[7]);
+          o1.x = pack_bf16x2(v[8], v[9]);   o1.y = pack_bf16x2(v[10], v[11]);
+          o1.z = pack_bf16x2(v[12], v[13]); o1.w = pack_bf16x2(v[14], v[15]);
+          uint4* dst = reinterpret_cast<uint4*>(buf + lane * 32);
+          dst[0] = o0;
+          dst[1] = o1;
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tm_y, buf, n, m0 + q * 32);
+            tma_store_commit();
+          }
+        }
+      } else if (m < p.M) {
         __nv_bfloat16* yrow = p.y + static_cast<int64_t>(m) * p.ldy;
 #pragma unroll
         for (int j = 0; j < C::kCols; j += 8) {
@@ -830,6 +881,7 @@ token_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
       }
     }
+    if (p.y_tma && lane == 0) tma_store_wait_all<0>();   // shared memory stays valid until the last stores have read it
   }
 
   // ------------------------------ teardown ------------------------------------
@@ -1455,6 +1507,12 @@ int run_token_pair(const GemmArgs& a, DeviceCtx* ctx) {
   p.splits = 1;
   p.y_vec = (a.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
   p.y_tma = 0;
+  CUtensorMap tm_y = tm_x;                                     // placeholder when TMA stores are not possible
+  if (p.y_vec) {
+    st = make_tmap_bf16_2d(&tm_y, a.y, a.M, a.N, a.ldy, 32, 16);
+    if (st != NQ_OK) return st;
+    p.y_tma = 1;
+  }
   p.sx_vec = (a.ld_sx % 4 == 0) && (reinterpret_cast<uintptr_t>(a.sx) % 16 == 0);
   p.wait_mode = 0;
   p.status = ctx->status_dev;
@@ -1477,7 +1535,7 @@ int run_token_pair(const GemmArgs& a, DeviceCtx* ctx) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = a.pdl ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, token_pair_kernel<BN>, tm_x, tm_w, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, token_pair_kernel<BN>, tm_x, tm_w, tm_y, p);
   count_launch();
   return check_cuda(e);
 }
@@ -1515,7 +1573,8 @@ int run_weight_lane(const GemmArgs& a, DeviceCtx* ctx, int splits) {
 }  // namespace
 
 int launch_gemm_token_pair(const GemmArgs& a, DeviceCtx* ctx, int tile_n) {
-  return tile_n == 128 ? run_token_pair<128>(a, ctx) : run_token_pair<256>(a, ctx);
+  (void)tile_n;
+  return run_token_pair<256>(a, ctx);
 }
 
 int launch_gemm_token_lane(const GemmArgs& a, DeviceCtx* ctx, int tile_n) {
@@ -1577,7 +1636,6 @@ int setup_gemm_kernels() {
 #define NQ_SET_SMEM(kern, bytes)                                                                  \
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);             \
   if (e != cudaSuccess) return check_cuda(e);
-  NQ_SET_SMEM(token_pair_kernel<128>, TokenPair<128>::kSmemBytes)
   NQ_SET_SMEM(token_pair_kernel<256>, TokenPair<256>::kSmemBytes)
   NQ_SET_SMEM(token_lane_kernel<128>, TokenLane<128>::kSmemBytes)
   NQ_SET_SMEM(token_lane_kernel<192>, TokenLane<192>::kSmemBytes)
@@ -1595,7 +1653,6 @@ int setup_gemm_kernels() {
   e = cudaFuncGetAttributes(&fa, kern);                                                           \
   if (e != cudaSuccess) return check_cuda(e);                                                     \
   if (fa.numRegs * ((threads) / 128) < (needed)) return NQ_ERR_UNSUPPORTED;
-  NQ_CHECK_REGS(token_pair_kernel<128>, TokenPair<128>::kThreads, TokenPair<128>::kRegsNeeded)
   NQ_CHECK_REGS(token_pair_kernel<256>, TokenPair<256>::kThreads, TokenPair<256>::kRegsNeeded)
   NQ_CHECK_REGS(token_lane_kernel<128>, TokenLane<128>::kThreads, TokenLane<128>::kRegsNeeded)
   NQ_CHECK_REGS(token_lane_kernel<192>, TokenLane<192>::kThreads, TokenLane<192>::kRegsNeeded)

@@ -11,7 +11,7 @@ import torch
 
 from . import _cabi
 from ._cabi import (ALGO_AUTO, ALGO_TOKEN_LANE, ALGO_TOKEN_LANE_128, ALGO_TOKEN_LANE_192,  # noqa: F401  (re-exported)
-                    ALGO_TOKEN_LANE_256, ALGO_TOKEN_PAIR, ALGO_TOKEN_PAIR_128, ALGO_WEIGHT_LANE,
+                    ALGO_TOKEN_LANE_256, ALGO_TOKEN_PAIR, ALGO_WEIGHT_LANE,
                     ALGO_WEIGHT_LANE_FUSED)
 
 GROUP = 128
