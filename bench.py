@@ -295,7 +295,9 @@ def run_gpu_arm(args) -> None:
     ops.init()
     tp = world
     if args.row_overlap_chunks is not None:
-        L.RowParallelLinear.overlap_chunks = args.row_overlap_chunks
+        if args.row_overlap_chunks > 0:
+            L.RowParallelLinear.sym_reduce = True
+            L.RowParallelLinear.overlap_chunks = args.row_overlap_chunks
     layers = build_stack(L, ops, rank, tp)
     torch.cuda.synchronize()
 
@@ -627,7 +629,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-batch-size sweep after the timed region")
     ap.add_argument("--row-overlap-chunks", type=int, default=None,
-                    help="token chunks in which row-parallel layers pipeline GEMM and all-reduce (default: the layer's own)")
+                    help="token chunks in which row-parallel layers overlap GEMM and peer-memory exchange (default: the "
+                         "0: one GEMM followed by NCCL's all-reduce)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

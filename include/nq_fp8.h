@@ -205,32 +205,25 @@ int nq_row_reduce_p2p(const void* partial, void* y, int64_t count,
                       void* const* inbox, int rank, int tp,
                       int64_t slot_bytes, void* state, void* stream);
 
-/* ---- Row-parallel reduction inside the NVLink switch (NVLS), for prefill-sized outputs ------------------------
+/* ---- Row-parallel reduction over peer-mapped buffers, for prefill-sized outputs ----------------------------
  * Stands in for the same `dist.all_reduce(y)` (linear.py:154-155) when y is large.  The partial outputs of all
- * ranks live at the same offset of a buffer that is mapped on every GPU of the group and bound to one multicast
- * address (the host obtains both from its symmetric-memory allocator; this library only needs the pointers).
- * One kernel per rank: barrier, multimem.ld_reduce + multimem.st over the rank's slice (the sum is formed once,
- * in fp32, inside the switch and written into every GPU's copy, in place), barrier.  On return (stream order) the
- * local copy of the buffer holds the sum and no peer touches it any more.  All ranks end with the same bits.
- *   mc_ptr : multicast address of the message (count bf16 elements, count % 8 == 0, 16-byte aligned)
- *   pads   : HOST array of tp device pointers, entry r = rank r's signal pad (NQ_MC_PAD_BYTES, zero-filled once,
+ * ranks live at the same offset of a buffer that every GPU of the group has mapped (the host obtains the
+ * mappings from its symmetric-memory allocator; this library only needs the pointers).  One kernel per rank, a
+ * two-shot exchange in which every transfer is a pull (16-byte loads from the peers' buffers): rank r adds slice r
+ * of all ranks' partials in rank order in fp32, writes the sum to y and back into its own buffer, and after a
+ * barrier fetches the other slices' sums from their owners into y; a last barrier keeps every buffer intact until
+ * all peers have read it.  All ranks end with the same bits.
+ *   bufs   : HOST array of tp device pointers, entry r = the message in rank r's buffer as mapped in this process
+ *   y      : private result, count bf16 elements (count % 8 == 0), 16-byte aligned
+ *   pads   : HOST array of tp device pointers, entry r = rank r's signal pad (NQ_SYM_PAD_BYTES, zero-filled once,
  *            peer-mapped) as mapped in this process
  *   state  : 16 bytes of zero-filled device memory private to the rank (call counter; graph-replay safe)
- *   blocks : thread blocks to use, 1..NQ_MC_MAX_BLOCKS, THE SAME ON EVERY RANK (block b pairs with block b)
- * All ranks must make the same sequence of calls.  Waits are bounded (nq_set_wait_limit_ns); a peer that never
- * arrives yields NQ_ERR_DEVICE_TIMEOUT in nq_device_status (site 80 or 81, aux = the peer) and a wrong result. */
-#define NQ_MC_MAX_BLOCKS 160
-#define NQ_MC_PAD_BYTES (3 * NQ_MC_MAX_BLOCKS * NQ_P2P_MAX_RANKS * 4)
-int nq_row_reduce_mc(void* mc_ptr, int64_t count, void* const* pads, int rank, int tp, void* state,
-                     int blocks, void* stream);
-
-/* The same sum without multicast: a two-shot exchange over plain peer memory in which every transfer is a pull
- * (16-byte loads from the peers' buffers).  Rank r adds slice r of all ranks' partials in rank order in fp32,
- * writes the sum to y and back into its own buffer, and after a barrier fetches the other slices' sums from
- * their owners into y; a last barrier keeps every buffer intact until all peers have read it.
- *   bufs : HOST array of tp device pointers, entry r = the message in rank r's buffer as mapped in this process
- *   y    : private result, count bf16 elements, 16-byte aligned (the buffers themselves are left holding a mix)
- * tp must be 2, 4 or 8; pads / state / blocks as for nq_row_reduce_mc (sites 80..82 on a time-out). */
+ *   blocks : thread blocks to use, 1..NQ_SYM_MAX_BLOCKS, THE SAME ON EVERY RANK (block b pairs with block b)
+ * tp must be 2, 4 or 8.  All ranks must make the same sequence of calls.  Waits are bounded
+ * (nq_set_wait_limit_ns); a peer that never arrives yields NQ_ERR_DEVICE_TIMEOUT in nq_device_status (site 80..82,
+ * aux = the peer) and a wrong result. */
+#define NQ_SYM_MAX_BLOCKS 160
+#define NQ_SYM_PAD_BYTES (3 * NQ_SYM_MAX_BLOCKS * NQ_P2P_MAX_RANKS * 4)
 int nq_row_reduce_pull(void* const* bufs, void* y, int64_t count, void* const* pads, int rank, int tp,
                        void* state, int blocks, void* stream);
 

@@ -48,7 +48,6 @@ SIGNATURES = {
     "nq_p2p_release": (c_int, [c_void_p]),
     "nq_row_reduce_p2p": (c_int, [c_void_p, c_void_p, c_int64, POINTER(c_void_p), c_int, c_int,
                                   c_int64, c_void_p, c_void_p]),
-    "nq_row_reduce_mc": (c_int, [c_void_p, c_int64, POINTER(c_void_p), c_int, c_int, c_void_p, c_int, c_void_p]),
     "nq_row_reduce_pull": (c_int, [POINTER(c_void_p), c_void_p, c_int64, POINTER(c_void_p), c_int, c_int, c_void_p,
                                    c_int, c_void_p]),
     "nq_device_status": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]),

@@ -13,7 +13,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libnq_fp8.so")
-SOURCES = ["nq_quant.cu", "nq_gemm.cu", "nq_capi.cu", "nq_noalloc.cu", "nq_p2p.cu", "nq_mc.cu", "nq_fused_quant.cu"]
+SOURCES = ["nq_quant.cu", "nq_gemm.cu", "nq_capi.cu", "nq_noalloc.cu", "nq_p2p.cu", "nq_sym.cu", "nq_fused_quant.cu"]
 HEADERS = ["nq_ptx.cuh", "nq_internal.cuh", os.path.join("..", "..", "include", "nq_fp8.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -69,7 +69,9 @@ int ensure_init(DeviceCtx** out) {
       if (e != cudaSuccess) return check_cuda(e);
       c->status_host = static_cast<DeviceStatus*>(host);
       c->status_dev = static_cast<DeviceStatus*>(devp);
-      const int st = setup_gemm_kernels();
+      int st = setup_gemm_kernels();
+      if (st != NQ_OK) return st;
+      st = setup_sym_kernels();
       if (st != NQ_OK) return st;
       c->ready.store(true, std::memory_order_release);
     }

@@ -51,5 +51,6 @@ int launch_gemm_token_pair(const GemmArgs& a, DeviceCtx* ctx, int tile_n);   // 
 size_t weight_lane_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int weight_lane_pick_split(int64_t M, int64_t N, int64_t K, int sm_count);
 int setup_gemm_kernels();   // cudaFuncSetAttribute for the large dynamic shared memory
+int setup_sym_kernels();    // the same for the peer-memory reduction
 
 }  // namespace nq

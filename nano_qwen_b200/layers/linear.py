@@ -32,7 +32,7 @@ import torch.distributed as dist
 from torch import nn
 
 from .. import ops
-from . import p2p_reduce
+from . import p2p_reduce, sym_reduce
 from .quantized import QuantizedActivation
 
 BLOCK = 128
@@ -203,22 +203,26 @@ class QKVParallelLinear(ColumnParallelLinear):
 class RowParallelLinear(LinearBase):
     """Input features split across ranks; partial outputs summed (reference ``linear.py:131-156``).
 
-    The sum is NCCL's all-reduce, as in the reference, except for decode-sized outputs on an NCCL group of 2..8
-    ranks, which one kernel per rank sums over peer memory (``p2p_reduce``; same result on every rank, fp32
-    accumulation in rank order; ``RowParallelLinear.p2p_reduce = False`` or ``NQ_P2P_REDUCE=0`` keeps NCCL).
+    How the sum is formed depends on the size of the output (always the same bits on every rank):
 
-    Optionally (``overlap_chunks > 1``) the sum is pipelined against the GEMM for prefill-sized batches:
-    the token rows are processed in up to ``overlap_chunks`` chunks of at least ``overlap_min_rows``
-    rows, and the all-reduce of chunk *i* (NCCL's own stream) runs while the GEMM of chunk *i+1*
-    executes on the SMs the GEMM leaves free.  Off by default: on 2 B200s it measured slower than one
-    GEMM followed by one all-reduce (the chunked GEMMs lose more than the overlap wins).  Under
-    CUDA-graph capture (decode) the call is always a single GEMM + all-reduce, like the reference.
+    * decode-sized outputs on an NCCL group of 2..8 ranks: one kernel per rank pushes the partial into every peer's
+      inbox and adds what arrived, fp32 accumulation in rank order (``p2p_reduce``; ``p2p_reduce = False`` or
+      ``NQ_P2P_REDUCE=0`` keeps NCCL);
+    * anything else: NCCL's all-reduce, as in the reference;
+    * on request (``sym_reduce = True``), prefill-sized outputs (at least ``overlap_min_rows`` token rows, eager
+      mode, 2 / 4 / 8 ranks): the GEMM runs in up to ``overlap_chunks`` chunks of token rows that write their partial
+      output into a peer-mapped buffer, and the exchange of chunk *i* (``sym_reduce.py``: a two-shot sum done with
+      bulk copies over NVLink, 16 thread blocks on a second stream) runs beside the GEMM of chunk *i + 1*, which
+      leaves those SMs free.  Off by default: on 2 B200s the 36-layer prefill pass took 49.2 ms that way against
+      44.7 ms for one GEMM followed by NCCL (the exchange needs about 32 SMs to match NCCL's 152 us for 64 MiB, and
+      what the GEMM loses with those SMs is what the overlap wins).
     """
 
     p2p_reduce = True            # small outputs are summed over peer memory instead of NCCL (see p2p_reduce.py)
-    overlap_chunks = 1
-    overlap_min_rows = 2048
-    overlap_sm_reserve = 16      # SMs the chunk GEMMs leave to the all-reduce kernel that runs beside them
+    sym_reduce = False           # large outputs: chunked GEMM overlapped with a peer-memory exchange (see sym_reduce.py)
+    overlap_chunks = 4
+    overlap_min_rows = 2048      # smaller batches take one GEMM and one reduction
+    overlap_chunk_rows = 1024    # a chunk is never smaller than this (and always a multiple of 128 rows)
 
     def __init__(self, input_size: int, output_size: int, bias: bool = False):
         tp_size = dist.get_world_size()
@@ -239,27 +243,46 @@ class RowParallelLinear(LinearBase):
         if self.tp_size == 1:
             return self._linear(x, bias)
         rows = math.prod(x.shape[:-1])
-        chunks = 0 if isinstance(x, QuantizedActivation) else min(self.overlap_chunks, rows // self.overlap_min_rows)
-        if chunks < 2 or not x.is_cuda or torch.cuda.is_current_stream_capturing():
-            y = self._linear(x, bias)
-            reducer = p2p_reduce.get_reducer() if (self.p2p_reduce and x.is_cuda) else None
-            if reducer is not None and reducer.fits(y):
-                reducer.reduce_(y)           # decode-sized: one kernel over peer memory
-            else:
-                dist.all_reduce(y)
-            return y
-        x2 = x.reshape(rows, x.shape[-1])
-        y = torch.empty((rows, self.output_size), dtype=torch.bfloat16, device=x.device)
-        step = (rows + chunks - 1) // chunks
-        pending = []
-        old = ops.set_sm_reserve(self.overlap_sm_reserve)
+        if (self.sym_reduce and x.is_cuda and rows >= self.overlap_min_rows
+                and not torch.cuda.is_current_stream_capturing()):
+            sym = sym_reduce.get_reducer()
+            if sym is not None and sym.fits(rows, self.output_size):
+                return self._forward_overlapped(x, bias, rows, sym)
+        y = self._linear(x, bias)
+        reducer = p2p_reduce.get_reducer() if (self.p2p_reduce and x.is_cuda) else None
+        if reducer is not None and reducer.fits(y):
+            reducer.reduce_(y)               # decode-sized: one kernel over peer memory
+        else:
+            dist.all_reduce(y)
+        return y
+
+    def _forward_overlapped(self, x, bias, rows: int, sym) -> torch.Tensor:
+        """Chunks of token rows: GEMM of chunk i + 1 on the current stream beside the exchange of chunk i."""
+        if isinstance(x, QuantizedActivation):
+            xq, sx, lead = x.xq, x.sx, x.shape[:-1]
+        else:
+            x2 = x.reshape(rows, x.shape[-1])
+            if x2.dtype != torch.bfloat16:
+                x2 = x2.to(torch.bfloat16)
+            xq, sx = ops.act_quant(x2)                   # one quantiser launch for all chunks
+            lead = x.shape[:-1]
+        n = self.output_size
+        part = sym.partial(rows, n)
+        y = torch.empty((rows, n), dtype=torch.bfloat16, device=xq.device)
+        chunks = max(1, min(self.overlap_chunks, rows // self.overlap_chunk_rows))
+        step = ((rows + chunks - 1) // chunks + 127) // 128 * 128
+        main = torch.cuda.current_stream()
+        old = ops.set_sm_reserve(sym.blocks)             # the GEMMs leave the exchange kernel its SMs
         try:
             for lo in range(0, rows, step):
-                part = y[lo:lo + step]
-                ops.fp8_linear(x2[lo:lo + step], self.weight, self.weight_scale_inv, bias, out=part)
-                pending.append(dist.all_reduce(part, async_op=True))  # overlaps the next chunk's GEMM
+                hi = min(lo + step, rows)
+                ops.fp8_gemm(xq[lo:hi], sx[lo:hi], self.weight, self.weight_scale_inv, bias, out=part[lo:hi])
+                done = torch.cuda.Event()
+                done.record(main)
+                sym.stream.wait_event(done)
+                with torch.cuda.stream(sym.stream):
+                    sym.reduce_pull(part[lo:hi], y[lo:hi])
         finally:
             ops.set_sm_reserve(old)
-        for work in pending:
-            work.wait()
-        return y.view(*x.shape[:-1], self.output_size)
+        main.wait_stream(sym.stream)
+        return y.view(*lead, n)
