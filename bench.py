@@ -45,10 +45,10 @@ WORKLOAD = ("Qwen3-8B-shaped 36-layer FP8 linear stack: decode pass M=256 (CUDA 
             "chunked-prefill pass M=8192 per step")
 
 
-# DRAM traffic of the dominant kernel: one ncu capture of its qkv launch at M = 8192 read 77.4 MB and wrote 70.2 MB
+# DRAM traffic of the dominant kernel: one ncu capture of its qkv launch at M = 8192 read 81.0 MB and wrote 73.9 MB
 # for 159.4 MB of algorithmic bytes (e4m3 x, e4m3 W, bf16 y); the other three shapes of the pass are scaled by the
 # same ratio (operands are read once, y is written once).
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 147.6 / 159.4
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 154.9 / 159.4
 
 
 def prefill_gemm_traffic_bytes(layers) -> float:
@@ -406,7 +406,7 @@ def run_gpu_arm(args) -> None:
 
     ms_decode, mhz_decode = timed_with_clock(graph.replay, 40, 5)
     ms_prefill, _ = timed(lambda: run_pass(layers, dev["prefill"]), 3, 1)
-    # dominant kernel: the token-lane GEMM of the prefill pass, timed alone on pre-quantised activations
+    # dominant kernel: the GEMM of the prefill pass (256 x 256 tiles on CTA pairs), timed alone on pre-quantised activations
     pre = {name: ops.act_quant(dev["prefill"][name]) for name in KINDS}
 
     def prefill_gemms_only():
@@ -574,14 +574,14 @@ def run_gpu_arm(args) -> None:
                     "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
             "gpu_launches": launches,
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "token_lane_kernel (prefill-pass FP8 GEMM)",
+            "roofline": {"bound": "tensor", "kernel": "token_pair_kernel (prefill-pass FP8 GEMM, 256x256 tiles on CTA pairs)",
                          "achieved": kernel_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": kernel_tflops / fp8_peak,
                          "peak_note": f"2 x bf16_tflops_sustained of {peaks['source']} (the e4m3 UMMA rate is twice the "
                                       "bf16 rate); torch._scaled_mm per-tensor FP8 measured 3046 burst / 2618 sustained here",
                          "launches": n_gemm, "avg_launch_us": ms_gemm * 1e3 / max(n_gemm, 1),
                          "traffic": prefill_gemm_traffic_bytes(layers), "traffic_unit": "bytes per launch",
-                         "traffic_note": "ncu dram read+write of the qkv launch (147.6 MB for 159.4 MB algorithmic) "
+                         "traffic_note": "ncu dram read+write of the qkv launch (154.9 MB for 159.4 MB algorithmic) "
                                          "scaled to the mean of the four shapes of the pass"},
             "passes": {"decode_ms": ms_decode, "prefill_ms": ms_prefill, "prefill_gemm_only_ms": ms_gemm,
                        "decode_gemm_only_ms": ms_dec_gemm,

@@ -136,7 +136,13 @@ int gemm_dispatch(const GemmArgs& a, int algo) {
   if (st != NQ_OK) return st;
   // Measured crossover on B200 (CUDA graph, 8B layer shapes): weight rows on the lanes up to 64 tokens; at 128 tokens
   // the token-lane kernel with 128-wide tiles is ahead (71 us against 76 us for the four linears of a layer).
-  if (algo == NQ_ALGO_AUTO) algo = (a.M <= 64) ? NQ_ALGO_WEIGHT_LANE : NQ_ALGO_TOKEN_LANE;
+  // Prefill-sized launches with at least two rounds of 256 x 256 tiles go to the CTA-pair kernel: alone it runs
+  // level with the single-CTA kernel (2.0-2.1 PFLOP/s), inside a long power-capped step it is 1-2 % ahead
+  // (a third fewer operand bytes cross the L2 -> SM path; three interleaved runs of the 36-layer step each).
+  if (algo == NQ_ALGO_AUTO) {
+    algo = (a.M <= 64) ? NQ_ALGO_WEIGHT_LANE : NQ_ALGO_TOKEN_LANE;
+    if (a.M >= 2048 && ((a.M + 255) / 256) * ((a.N + 255) / 256) >= ctx->sm_count) algo = NQ_ALGO_TOKEN_PAIR;
+  }
   if (algo == NQ_ALGO_TOKEN_LANE) return launch_gemm_token_lane(a, ctx, 0);
   if (algo == NQ_ALGO_TOKEN_LANE_128) return launch_gemm_token_lane(a, ctx, 128);
   if (algo == NQ_ALGO_TOKEN_LANE_192) return launch_gemm_token_lane(a, ctx, 192);
