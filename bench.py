@@ -545,6 +545,33 @@ def run_gpu_arm(args) -> None:
             detail["producers"][str(m)] = res
             del gu, xr
         torch.cuda.synchronize()
+        # ---- context: what the reference's own GPU path costs on this box.  nano_qwen's layers are bf16 ``F.linear``
+        #      (cuBLAS) followed, for row layers, by ``dist.all_reduce`` (layers/linear.py:72-73, :152-156); four layers'
+        #      worth of bf16 weights of this rank's shard shapes are cycled (they exceed L2), same token counts ----
+        import torch.nn.functional as F
+        shapes_r = {"qkv": (HIDDEN, (HEADS + 2 * KV_HEADS) * HEAD_DIM // tp), "o_proj": (HIDDEN // tp, HIDDEN),
+                    "gate_up": (HIDDEN, 2 * INTER // tp), "down": (INTER // tp, HIDDEN)}
+        n_ref = 4
+        wref = [{name: (torch.randn((n, k), generator=gen_d, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                 for name, (k, n) in shapes_r.items()} for _ in range(n_ref)]
+        detail["bf16_f_linear"] = {}
+        for m in (M_DECODE, M_PREFILL):
+            xs = {name: torch.randn((m, k), generator=gen_d, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+                  for name, (k, n) in shapes_r.items()}
+
+            def ref_pass():
+                for wl in wref:
+                    for name in KINDS:
+                        y = F.linear(xs[name], wl[name])
+                        if tp > 1 and name in ("o_proj", "down"):
+                            dist.all_reduce(y)
+            ms, _ = timed(ref_pass, 3, 2)
+            layer_us = ms * 1e3 / n_ref
+            detail["bf16_f_linear"][str(m)] = {"layer_us": round(layer_us, 2),
+                                               "tflops": round(FLOPS_PER_TOKEN_LAYER * m / (layer_us * 1e-6) / 1e12, 1)}
+            del xs
+        del wref
+        torch.cuda.synchronize()
     status = _cabi.device_status()
 
     if rank == 0:
@@ -592,7 +619,9 @@ def run_gpu_arm(args) -> None:
             "detail": {"note": "one pass of the same stack per batch size M: act quant + GEMM (+ all-reduce) per linear; "
                                "layer_us = pass time / 36 (layer_32b: one Qwen3-32B-shaped layer at this TP degree, three "
                                "weight copies cycled); hbm_gbs_per_gpu uses the algorithmic bytes of one rank's layer "
-                               f"(measured copy peak {peaks['hbm_gbs']} GB/s); tflops is the whole job",
+                               f"(measured copy peak {peaks['hbm_gbs']} GB/s); tflops is the whole job; bf16_f_linear: "
+                               "the reference's own GPU path (cuBLAS bf16 F.linear + NCCL all-reduce, eager) on the same "
+                               "shard shapes, for context",
                        **detail},
             "device_status": status["code"],
         }
