@@ -80,35 +80,56 @@ int ensure_init(DeviceCtx** out) {
   return NQ_OK;
 }
 
-int make_tmap_u8_2d(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
-  const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+namespace {
+// Tensor maps are pure functions of (base, extents, stride, box, type): the weights of a layer and the static
+// buffers of a CUDA-graph runner come back with the same arguments on every call, so the driver's encoder
+// (1-2 us per map) is asked once per distinct argument set.  Small direct-mapped cache, one per thread.
+struct TmapKey {
+  const void* base; int64_t rows, cols, ld; int box_rows, box_cols, kind;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+           box_cols == o.box_cols && kind == o.kind;
+  }
+};
+struct TmapSlot { TmapKey key; CUtensorMap map; bool valid; };
+constexpr int kTmapSlots = 1024;
+thread_local TmapSlot t_tmap_cache[kTmapSlots];
+
+int cached_encode(CUtensorMap* out, const TmapKey& k) {
+  uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<uint64_t>(k.rows) * 0xC2B2AE3D27D4EB4Full + static_cast<uint64_t>(k.cols) * 0x165667B19E3779F9ull;
+  h ^= static_cast<uint64_t>(k.ld) * 0x27D4EB2F165667C5ull + static_cast<uint64_t>(k.box_rows * 4 + k.box_cols * 4096 + k.kind);
+  TmapSlot& slot = t_tmap_cache[(h >> 32) % kTmapSlots];
+  if (slot.valid && slot.key == k) { *out = slot.map; return NQ_OK; }
+  const bool u8 = (k.kind == 0);
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k.cols), static_cast<cuuint64_t>(k.rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k.ld) * (u8 ? 1 : 2)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(k.box_cols), static_cast<cuuint32_t>(k.box_rows)};
   const cuuint32_t elem[2] = {1u, 1u};
-  const CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = g_encode(out, u8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                              const_cast<void*>(k.base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              u8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                              u8 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    snprintf(t_cuda_err, sizeof(t_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    snprintf(t_cuda_err, sizeof(t_cuda_err), "cuTensorMapEncodeTiled (%s) failed with CUresult %d", u8 ? "u8" : "bf16",
+             static_cast<int>(r));
     return NQ_ERR_CUDA;
   }
+  slot.key = k;
+  slot.map = *out;
+  slot.valid = true;
   return NQ_OK;
+}
+}  // namespace
+
+int make_tmap_u8_2d(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  return cached_encode(out, TmapKey{base, rows, cols, ld, box_rows, 128, 0});
 }
 
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows,
                       int box_cols) {
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
-  const cuuint32_t elem[2] = {1u, 1u};
-  const CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    snprintf(t_cuda_err, sizeof(t_cuda_err), "cuTensorMapEncodeTiled (bf16) failed with CUresult %d", static_cast<int>(r));
-    return NQ_ERR_CUDA;
-  }
-  return NQ_OK;
+  return cached_encode(out, TmapKey{base, rows, cols, ld, box_rows, box_cols, 1});
 }
 
 namespace {
