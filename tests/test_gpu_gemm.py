@@ -168,6 +168,21 @@ def test_auto_dispatch_on_seeded_random_shapes(ops):
         check(run_gemm(ops, case, ops.ALGO_AUTO), case)
 
 
+def test_auto_takes_cta_pairs_for_prefill_sizes_with_ragged_edges(ops):
+    """Prefill-sized launches (>= 2048 tokens and at least one 256 x 256 tile per SM) run on CTA pairs under
+    NQ_ALGO_AUTO: ragged M and N, a K that is not a multiple of 128, bias; also with SMs held back for a neighbour."""
+    case = make_case(2048 + 75, 4096 + 136, 640 + 16, seed=77, bias=True)       # 9 x 17 tiles of 256 x 256 = 153 >= 148
+    a = run_gemm(ops, case, ops.ALGO_AUTO)
+    check(a, case)
+    assert torch.equal(a.view(torch.int16), run_gemm(ops, case, ops.ALGO_TOKEN_PAIR).view(torch.int16))
+    old = ops.set_sm_reserve(20)
+    try:
+        b = run_gemm(ops, case, ops.ALGO_AUTO)
+    finally:
+        ops.set_sm_reserve(old)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))              # the grid size does not change the sums
+
+
 def test_results_are_deterministic(ops):
     case = make_case(48, 1024, 4096, seed=5)
     a = run_gemm(ops, case, ops.ALGO_WEIGHT_LANE, split_k=4)
