@@ -66,7 +66,7 @@ extern "C" {
 #define NQ_ALGO_WEIGHT_LANE_FUSED 8 /* nq_fp8_linear only: weight-lane with the activation quantiser inside the GEMM
                                        kernel (M <= NQ_FUSED_MAX_TOKENS, K and ldx multiples of 8, x 16-byte aligned) */
 #define NQ_FUSED_MAX_TOKENS 32  /* most tokens NQ_ALGO_WEIGHT_LANE_FUSED accepts */
-#define NQ_FUSED_AUTO_TOKENS 8  /* most tokens for which NQ_ALGO_AUTO picks it */
+#define NQ_FUSED_AUTO_TOKENS 0  /* most tokens for which NQ_ALGO_AUTO picks it: none (see nq_fp8_linear) */
 
 /* ABI version of this header (major*100 + minor). */
 int nq_version(void);
@@ -140,10 +140,13 @@ int nq_fp8_gemm_bs128(const void* xq, int64_t ld_xq, const float* sx, int64_t ld
 /* Convenience: activation quantiser + GEMM in one call.  `xq_scratch`
  * (M*ld_xq bytes, ld_xq = K rounded up to 16) and `sx_scratch`
  * (ceil(K/128)*ld_sx floats, ld_sx = M rounded up to 4) are caller-owned.
- * With NQ_ALGO_AUTO and M <= NQ_FUSED_AUTO_TOKENS the quantiser runs inside the
- * GEMM kernel (NQ_ALGO_WEIGHT_LANE_FUSED: one launch, scratch untouched and
- * allowed to be NULL) whenever x can be read 16 bytes at a time; the result is
- * bit-identical to the two-launch path, which NQ_ALGO_WEIGHT_LANE still selects. */
+ * NQ_ALGO_WEIGHT_LANE_FUSED (M <= NQ_FUSED_MAX_TOKENS, x readable 16 bytes at a
+ * time) runs the quantiser inside the GEMM kernel: one launch, scratch untouched
+ * and allowed to be NULL, result bit-identical to the two-launch path.
+ * NQ_ALGO_AUTO does not pick it any more: since the quantiser kernel releases its
+ * dependents at its start (programmatic dependent launch), the GEMM's set-up and
+ * first weight tiles overlap the quantiser, and two launches measured faster at
+ * every batch size (8 tokens: 47.9 us per 8B-shaped layer against 58.0 us). */
 int nq_fp8_linear(const void* x, int64_t ldx,
                   const void* wq, int64_t ld_wq, const float* sw, int64_t ld_sw,
                   const void* bias, void* y, int64_t ldy,

@@ -16,7 +16,7 @@ ALGO_AUTO, ALGO_TOKEN_LANE, ALGO_WEIGHT_LANE = 0, 1, 2
 ALGO_TOKEN_LANE_128, ALGO_TOKEN_LANE_192, ALGO_TOKEN_LANE_256 = 3, 4, 5
 ALGO_TOKEN_PAIR = 6
 ALGO_WEIGHT_LANE_FUSED = 8
-FUSED_MAX_TOKENS, FUSED_AUTO_TOKENS = 32, 8      # NQ_FUSED_MAX_TOKENS, NQ_FUSED_AUTO_TOKENS
+FUSED_MAX_TOKENS, FUSED_AUTO_TOKENS = 32, 0      # NQ_FUSED_MAX_TOKENS, NQ_FUSED_AUTO_TOKENS
 
 # name -> (restype, argtypes); every symbol include/nq_fp8.h declares
 SIGNATURES = {

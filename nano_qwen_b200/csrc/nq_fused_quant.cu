@@ -68,6 +68,7 @@ __device__ __forceinline__ uint4 pack8_bf16(const float* v) {
 __global__ void __launch_bounds__(256) silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, int64_t M, int64_t I,
                                                              int64_t ld, uint8_t* __restrict__ xq, int64_t ld_xq,
                                                              float* __restrict__ sx, int64_t ld_sx) {
+  pdl_launch_next();   // the consumer GEMM sets up and prefetches weights meanwhile; it waits for this grid itself
   pdl_wait_prior();
   const int64_t G = (I + 127) >> 7;
   const int64_t items = M * G;
@@ -99,7 +100,6 @@ __global__ void __launch_bounds__(256) silu_mul_quant_kernel(const __nv_bfloat16
     if (l8 == 0) sx[g * ld_sx + m] = scale;
     if (k0 < I) *reinterpret_cast<uint4*>(xq + m * ld_xq + k0) = q;
   }
-  pdl_launch_next();
 }
 
 // One CTA of 256 threads per token row.  Pass 1: x (+ residual) in fp32, sum of squares.  Pass 2 reads the row again
@@ -112,6 +112,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __nv_bfloat16*
                                                             int64_t ld_xq, float* __restrict__ sx, int64_t ld_sx) {
   __shared__ float warp_sum[8];
   __shared__ float s_rstd;
+  pdl_launch_next();   // the consumer GEMM sets up and prefetches weights meanwhile; it waits for this grid itself
   pdl_wait_prior();
   const int64_t m = blockIdx.x;
   const int64_t G = (H + 127) >> 7;
@@ -192,7 +193,6 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __nv_bfloat16*
     if (l8 == 0 && (g << 7) < H) sx[g * ld_sx + m] = scale;
     if (in) *reinterpret_cast<uint4*>(xq + m * ld_xq + k0) = q;
   }
-  pdl_launch_next();
 }
 
 bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

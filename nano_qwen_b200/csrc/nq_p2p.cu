@@ -71,6 +71,10 @@ __global__ void __launch_bounds__(kThreads) row_reduce_p2p_kernel(const RowReduc
   __shared__ int s_abort;
   const int b = blockIdx.x, tid = threadIdx.x;
   if (tid == 0) s_abort = 0;
+  // Programmatic dependent launch: the kernel behind this one may start its set-up now; this one waits for the GEMM
+  // that produces `src` before it reads anything.
+  pdl_launch_next();
+  pdl_wait_prior();
   __syncthreads();
   const uint64_t call = *reinterpret_cast<volatile uint64_t*>(p.state) + 1ull;   // number of this call, 1-based
   const uint32_t e = static_cast<uint32_t>(call % 0xFFFFFFFFull) + 1u;           // tag in the words: 1 .. 2^32 - 1
@@ -222,9 +226,19 @@ int nq_row_reduce_p2p(const void* partial, void* y, int64_t count, void* const* 
   int64_t blocks = (p.n16 + kThreads - 1) / kThreads;
   const int64_t cap = 2 * ctx->sm_count;
   if (blocks > cap) blocks = cap;
-  row_reduce_p2p_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, row_reduce_p2p_kernel, p);
   count_launch();
-  return check_cuda(cudaGetLastError());
+  return check_cuda(e);
 }
 
 }  // extern "C"

@@ -21,6 +21,9 @@ template <bool VEC>
 __global__ void __launch_bounds__(256) act_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t K,
                                                         int64_t ldx, uint8_t* __restrict__ xq, int64_t ld_xq,
                                                         float* __restrict__ sx, int64_t ld_sx) {
+  // Let the GEMM that follows start at once: its set-up and its first weight tiles do not depend on this kernel (it
+  // waits for this grid's completion itself, with griddepcontrol.wait, before it touches xq / sx).
+  pdl_launch_next();
   pdl_wait_prior();
   const int64_t G = (K + 127) >> 7;
   const int64_t items = M * G;
@@ -97,7 +100,6 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __nv_bfloat16* __r
         if (k0 + i < K) xq[m * ld_xq + k0 + i] = static_cast<uint8_t>(qw[i >> 2] >> ((i & 3) * 8));
     }
   }
-  pdl_launch_next();
 }
 
 // ------------------------------------------------------------------------- //

@@ -82,19 +82,20 @@ def test_fused_outlier_rows_and_zero_rows(ops, m):
     check_oracle(one, x, wq, sw, b)
 
 
-def test_auto_takes_one_launch_for_a_handful_of_tokens_and_two_above(ops):
-    from nano_qwen_b200._cabi import FUSED_AUTO_TOKENS as T
+def test_fused_on_request_is_one_launch_and_auto_is_two_with_the_same_bits(ops):
+    """NQ_ALGO_AUTO keeps quantiser and GEMM as two launches at every batch size (the GEMM's set-up overlaps the
+    quantiser through programmatic dependent launch, which measured faster); the one-launch kernel stays selectable."""
+    T = 8
     x, wq, sw, b = make(T, 1024, 1024, seed=1, bias=False)
     xd, wd, sd = x.cuda(), wq.cuda(), sw.cuda()
     n0 = ops.launch_count()
-    y_few = ops.fp8_linear(xd, wd, sd)
+    y_fused = ops.fp8_linear(xd, wd, sd, algo=ops.ALGO_WEIGHT_LANE_FUSED)
     n1 = ops.launch_count()
     assert n1 - n0 == 1
-    x2 = torch.cat([xd, xd[:1]])
-    y_more = ops.fp8_linear(x2, wd, sd)
+    y_auto = ops.fp8_linear(xd, wd, sd)
     assert ops.launch_count() - n1 == 2
     torch.cuda.synchronize()
-    assert torch.equal(y_more[:T].cpu(), y_few.cpu())
+    assert torch.equal(y_auto.cpu(), y_fused.cpu())
 
 
 def test_strided_rows_and_guarded_output(ops):
