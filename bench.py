@@ -450,7 +450,8 @@ def run_gpu_arm(args) -> None:
                 gm = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gm):
                     run_pass(layers, xs)
-                ms, mhz = timed_with_clock(gm.replay, 20, 3)
+                # enough warm-up replays (50-100 ms) for the SM clock to come back up after the power-capped passes
+                ms, mhz = timed_with_clock(gm.replay, 20, 40)
                 del gm
             else:
                 ms, mhz = timed_with_clock(lambda: run_pass(layers, xs), 2, 1)

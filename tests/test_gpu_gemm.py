@@ -75,7 +75,7 @@ def test_weight_lane_matches_oracle(ops, m, n, k):
 
 
 @pytest.mark.parametrize("split", [1, 2, 4, 8])
-@pytest.mark.parametrize("m", [3, 64, 130])
+@pytest.mark.parametrize("m", [3, 16, 24, 64, 130])
 def test_weight_lane_split_k(ops, split, m):
     case = make_case(m, 512, 2048, seed=split, bias=True)
     check(run_gemm(ops, case, ops.ALGO_WEIGHT_LANE, split_k=split), case)
