@@ -142,6 +142,19 @@ def run_reference_arm(args) -> None:
 # --------------------------------------------------------------------------- #
 # GPU arm                                                                      #
 # --------------------------------------------------------------------------- #
+def row_sum_note(L, tp: int) -> str:
+    """Which reduction the row-parallel layers of this run use (decode-sized / prefill-sized outputs)."""
+    if tp == 1:
+        return "none (tp 1)"
+    from nano_qwen_b200.layers import p2p_reduce, sym_reduce
+    cls = L.RowParallelLinear
+    small = "peer-memory push kernel" if (cls.p2p_reduce and p2p_reduce._reducer is not None) else "NCCL"
+    want = cls.sym_reduce if cls.sym_reduce is not None else tp == 8
+    large = (f"peer-memory pull kernel ({cls.overlap_chunks} chunk(s))"
+             if (want and sym_reduce._reducer is not None) else "NCCL all-reduce")
+    return f"decode-sized: {small}; prefill-sized: {large}"
+
+
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -294,9 +307,9 @@ def run_gpu_arm(args) -> None:
     from nano_qwen_b200.layers import linear as L
     ops.init()
     tp = world
-    if args.row_overlap_chunks is not None:
+    if args.row_overlap_chunks is not None:                 # default: the layer's own choice (peer-memory sum on 8 ranks)
+        L.RowParallelLinear.sym_reduce = args.row_overlap_chunks > 0
         if args.row_overlap_chunks > 0:
-            L.RowParallelLinear.sym_reduce = True
             L.RowParallelLinear.overlap_chunks = args.row_overlap_chunks
     layers = build_stack(L, ops, rank, tp)
     torch.cuda.synchronize()
@@ -597,7 +610,8 @@ def run_gpu_arm(args) -> None:
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "tp": tp, "layers": LAYERS,
-                       "l2": "weights of the stack (6.95 GB / tp) exceed L2; no flush needed"},
+                       "l2": "weights of the stack (6.95 GB / tp) exceed L2; no flush needed",
+                       "row_parallel_sum": row_sum_note(L, tp)},
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
             "gpu_launches": launches,
@@ -659,8 +673,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-batch-size sweep after the timed region")
     ap.add_argument("--row-overlap-chunks", type=int, default=None,
-                    help="token chunks in which row-parallel layers overlap GEMM and peer-memory exchange (default: the "
-                         "0: one GEMM followed by NCCL's all-reduce)")
+                    help="row-parallel layers at prefill sizes: N > 0 = sum over the peer-mapped buffer, the GEMM in N "
+                         "chunks of token rows (N > 1: exchange of a chunk beside the GEMM of the next); 0 = NCCL's "
+                         "all-reduce; default: the layer's own choice (peer-mapped buffer on 8 ranks, one chunk)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -208,19 +208,21 @@ class RowParallelLinear(LinearBase):
     * decode-sized outputs on an NCCL group of 2..8 ranks: one kernel per rank pushes the partial into every peer's
       inbox and adds what arrived, fp32 accumulation in rank order (``p2p_reduce``; ``p2p_reduce = False`` or
       ``NQ_P2P_REDUCE=0`` keeps NCCL);
-    * anything else: NCCL's all-reduce, as in the reference;
-    * on request (``sym_reduce = True``), prefill-sized outputs (at least ``overlap_min_rows`` token rows, eager
-      mode, 2 / 4 / 8 ranks): the GEMM runs in up to ``overlap_chunks`` chunks of token rows that write their partial
-      output into a peer-mapped buffer, and the exchange of chunk *i* (``sym_reduce.py``: a two-shot sum done with
-      bulk copies over NVLink, 16 thread blocks on a second stream) runs beside the GEMM of chunk *i + 1*, which
-      leaves those SMs free.  Off by default: on 2 B200s the 36-layer prefill pass took 49.2 ms that way against
-      44.7 ms for one GEMM followed by NCCL (the exchange needs about 32 SMs to match NCCL's 152 us for 64 MiB, and
-      what the GEMM loses with those SMs is what the overlap wins).
+    * prefill-sized outputs (at least ``overlap_min_rows`` token rows, eager mode) on 8 ranks, or on 2 / 4 ranks on
+      request (``sym_reduce = True``): the GEMM writes its partial output into a peer-mapped buffer and one kernel
+      per rank sums it over the group (``sym_reduce.py``: a two-shot exchange done with bulk copies over NVLink, 32
+      thread blocks).  Measured on 8 B200s for 64 MiB: 219 us against NCCL's 274 us; the 36-layer prefill + decode
+      step 32.1 ms against 35.3 ms.  ``sym_reduce = False`` or ``NQ_SYM_REDUCE=0`` keeps NCCL;
+    * anything else: NCCL's all-reduce, as in the reference.
+
+    With ``overlap_chunks`` > 1 the GEMM runs in chunks of token rows and the exchange of chunk *i* runs on a second
+    stream beside the GEMM of chunk *i + 1*, which leaves it its SMs.  Measured slower than one GEMM followed by one
+    exchange (2 ranks: 49.2 ms against 44.7 ms with NCCL; 8 ranks: 33.2 ms against 32.1 ms), so the default is one chunk.
     """
 
     p2p_reduce = True            # small outputs are summed over peer memory instead of NCCL (see p2p_reduce.py)
-    sym_reduce = False           # large outputs: chunked GEMM overlapped with a peer-memory exchange (see sym_reduce.py)
-    overlap_chunks = 4
+    sym_reduce = None            # large outputs over a peer-mapped buffer (see sym_reduce.py): None = on 8 ranks only
+    overlap_chunks = 1
     overlap_min_rows = 2048      # smaller batches take one GEMM and one reduction
     overlap_chunk_rows = 1024    # a chunk is never smaller than this (and always a multiple of 128 rows)
 
@@ -243,7 +245,8 @@ class RowParallelLinear(LinearBase):
         if self.tp_size == 1:
             return self._linear(x, bias)
         rows = math.prod(x.shape[:-1])
-        if (self.sym_reduce and x.is_cuda and rows >= self.overlap_min_rows
+        use_sym = self.sym_reduce if self.sym_reduce is not None else self.tp_size == 8
+        if (use_sym and x.is_cuda and rows >= self.overlap_min_rows
                 and not torch.cuda.is_current_stream_capturing()):
             sym = sym_reduce.get_reducer()
             if sym is not None and sym.fits(rows, self.output_size):
@@ -257,7 +260,8 @@ class RowParallelLinear(LinearBase):
         return y
 
     def _forward_overlapped(self, x, bias, rows: int, sym) -> torch.Tensor:
-        """Chunks of token rows: GEMM of chunk i + 1 on the current stream beside the exchange of chunk i."""
+        """The partial output goes to the peer-mapped buffer and is summed from there; with several chunks of token
+        rows, the GEMM of chunk i + 1 runs on the current stream beside the exchange of chunk i."""
         if isinstance(x, QuantizedActivation):
             xq, sx, lead = x.xq, x.sx, x.shape[:-1]
         else:
@@ -270,6 +274,10 @@ class RowParallelLinear(LinearBase):
         part = sym.partial(rows, n)
         y = torch.empty((rows, n), dtype=torch.bfloat16, device=xq.device)
         chunks = max(1, min(self.overlap_chunks, rows // self.overlap_chunk_rows))
+        if chunks == 1:                                  # one GEMM on every SM, then one exchange, on this stream
+            ops.fp8_gemm(xq, sx, self.weight, self.weight_scale_inv, bias, out=part)
+            sym.reduce_pull(part, y)
+            return y.view(*lead, n)
         step = ((rows + chunks - 1) // chunks + 127) // 128 * 128
         main = torch.cuda.current_stream()
         old = ops.set_sm_reserve(sym.blocks)             # the GEMMs leave the exchange kernel its SMs

@@ -4,8 +4,10 @@ Stands in for the ``dist.all_reduce(y)`` that ends the reference's ``RowParallel
 (``nano_qwen/layers/linear.py:154-155``) when ``y`` is large.  The row-parallel GEMM writes its partial output
 straight into a buffer that every GPU of the group has mapped; one kernel per rank then sums its slice of the
 message from all peers and collects the other slices' sums (a two-shot exchange done with loads over NVLink).
-The kernel needs only a few dozen thread blocks, so it runs on a second stream beside the GEMM of the next chunk
-of token rows: that overlap, not the exchange itself (on a par with NCCL), is what the layer gains.
+Measured on B200s for 64 MiB: 219 us on 8 GPUs with 32 thread blocks (more do not help) against NCCL's 274 us;
+140 us on 2 GPUs against 152 us.  The kernel needs only a few dozen thread blocks, so it can also run on a second
+stream beside the GEMM of the next chunk of token rows; that overlap measured slower than one GEMM followed by one
+exchange and is off by default.
 
 ``torch.distributed`` is the plumbing: its symmetric-memory allocator provides the peer-mapped buffer and the
 rendezvous between the ranks; the kernels only see raw pointers.  All ranks must be processes on one node, one
@@ -28,7 +30,7 @@ DEFAULT_CAPACITY = 192 << 20        # bytes of partial output the buffer can hol
 class SymRowReducer:
     """One per process: the symmetric partial-output buffer, signal pads, call counter and the side stream."""
 
-    def __init__(self, capacity_bytes: int = DEFAULT_CAPACITY, group=None, blocks: int = 16):
+    def __init__(self, capacity_bytes: int = DEFAULT_CAPACITY, group=None, blocks: int = 32):
         import torch.distributed._symmetric_memory as symm_mem
         pg = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(pg)
@@ -96,7 +98,7 @@ def get_reducer() -> SymRowReducer | None:
         return None                                     # set-up allocates and talks to the peers: not during a capture
     try:
         _reducer = SymRowReducer(int(os.environ.get("NQ_SYM_REDUCE_BYTES", DEFAULT_CAPACITY)),
-                                 blocks=int(os.environ.get("NQ_SYM_REDUCE_BLOCKS", 16)))
+                                 blocks=int(os.environ.get("NQ_SYM_REDUCE_BLOCKS", 32)))
     except Exception as exc:                            # no symmetric memory on this system: the reference's collective stays
         import warnings
         warnings.warn(f"peer-memory row reduction unavailable, keeping NCCL: {exc}")

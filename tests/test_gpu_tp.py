@@ -77,20 +77,24 @@ def _worker(rank, world, port, out_path, ckpt_dir):
             torch.cuda.synchronize()
             res[name + "_graph"] = yg.clone()
             del g, yg                                       # a graph holding an NCCL collective pins the communicator
-        # prefill-sized batch: chunked GEMMs overlapped with the peer-memory exchange (on request) against one
-        # GEMM followed by NCCL's all-reduce (the default, the reference's sequence)
+        # prefill-sized batch: the sum over the peer-mapped buffer (one GEMM then one exchange: the default on 8
+        # ranks; chunked GEMMs overlapped with the exchange on request) against one GEMM followed by NCCL's
+        # all-reduce (the reference's sequence)
         big = torch.randn(4096 + 200, shapes["down"][0] // world, generator=torch.Generator().manual_seed(5 + rank)).to(torch.bfloat16).cuda()
         row = rows["down"]
+        row.sym_reduce = False
         single = row(big)
         row.sym_reduce = True
+        one = row(big)
+        row.overlap_chunks = 4
         piped = row(big)                                  # 4 chunks; the last one ragged
         row.overlap_chunks = 2
         piped2 = row(big)
-        row.overlap_chunks = 4
-        row.sym_reduce = False
+        row.overlap_chunks = 1
+        row.sym_reduce = None
         torch.cuda.synchronize()
         # same sums up to fp32 summation order and NCCL's bf16 rounding of partial sums along its ring
-        err = max(float((t.float() - single.float()).abs().max() / single.float().abs().max()) for t in (piped, piped2))
+        err = max(float((t.float() - single.float()).abs().max() / single.float().abs().max()) for t in (one, piped, piped2))
         res["pipelined_close_to_single"] = torch.tensor([1 if err <= (8e-3 if world == 2 else 2e-2) else 0], dtype=torch.int16)
         res["pipelined_for_rank_equality"] = piped.reshape(-1)[::97].clone()
         # ---- Qwen3-32B-shaped row layer (down_proj, K = 25600 split over the ranks) against the unsharded product ----
