@@ -149,7 +149,7 @@ def row_sum_note(L, tp: int) -> str:
     from nano_qwen_b200.layers import p2p_reduce, sym_reduce
     cls = L.RowParallelLinear
     small = "peer-memory push kernel" if (cls.p2p_reduce and p2p_reduce._reducer is not None) else "NCCL"
-    want = cls.sym_reduce if cls.sym_reduce is not None else tp == 8
+    want = cls.sym_reduce if cls.sym_reduce is not None else tp in cls.sym_auto_ranks
     large = (f"peer-memory pull kernel ({cls.overlap_chunks} chunk(s))"
              if (want and sym_reduce._reducer is not None) else "NCCL all-reduce")
     return f"decode-sized: {small}; prefill-sized: {large}"
@@ -307,12 +307,21 @@ def run_gpu_arm(args) -> None:
     from nano_qwen_b200.layers import linear as L
     ops.init()
     tp = world
-    if args.row_overlap_chunks is not None:                 # default: the layer's own choice (peer-memory sum on 8 ranks)
+    if args.row_overlap_chunks is not None:                 # default: the layer's own choice (peer-memory sum on 2 and 8 ranks)
         L.RowParallelLinear.sym_reduce = args.row_overlap_chunks > 0
         if args.row_overlap_chunks > 0:
             L.RowParallelLinear.overlap_chunks = args.row_overlap_chunks
     layers = build_stack(L, ops, rank, tp)
     torch.cuda.synchronize()
+    if tp > 1:
+        # collective set-up of the peer-memory reductions, as a model runner does it once after init_process_group
+        # and before graph capture (otherwise the first forward of each kind would do it, inside a warm-up step)
+        from nano_qwen_b200.layers import p2p_reduce, sym_reduce
+        if L.RowParallelLinear.p2p_reduce:
+            p2p_reduce.init()
+        want_sym = L.RowParallelLinear.sym_reduce
+        if want_sym if want_sym is not None else tp in L.RowParallelLinear.sym_auto_ranks:
+            sym_reduce.init()
 
     gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
     host = {}
@@ -675,7 +684,7 @@ def main():
     ap.add_argument("--row-overlap-chunks", type=int, default=None,
                     help="row-parallel layers at prefill sizes: N > 0 = sum over the peer-mapped buffer, the GEMM in N "
                          "chunks of token rows (N > 1: exchange of a chunk beside the GEMM of the next); 0 = NCCL's "
-                         "all-reduce; default: the layer's own choice (peer-mapped buffer on 8 ranks, one chunk)")
+                         "all-reduce; default: the layer's own choice (peer-mapped buffer on 2 and 8 ranks, one chunk)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -208,11 +208,14 @@ class RowParallelLinear(LinearBase):
     * decode-sized outputs on an NCCL group of 2..8 ranks: one kernel per rank pushes the partial into every peer's
       inbox and adds what arrived, fp32 accumulation in rank order (``p2p_reduce``; ``p2p_reduce = False`` or
       ``NQ_P2P_REDUCE=0`` keeps NCCL);
-    * prefill-sized outputs (at least ``overlap_min_rows`` token rows, eager mode) on 8 ranks, or on 2 / 4 ranks on
+    * prefill-sized outputs (at least ``overlap_min_rows`` token rows, eager mode) on 2 or 8 ranks, or on 4 ranks on
       request (``sym_reduce = True``): the GEMM writes its partial output into a peer-mapped buffer and one kernel
       per rank sums it over the group (``sym_reduce.py``: a two-shot exchange done with bulk copies over NVLink, 32
-      thread blocks).  Measured on 8 B200s for 64 MiB: 219 us against NCCL's 274 us; the 36-layer prefill + decode
-      step 32.1 ms against 35.3 ms.  ``sym_reduce = False`` or ``NQ_SYM_REDUCE=0`` keeps NCCL;
+      thread blocks).  Measured on B200s for 64 MiB: 219 us against NCCL's 274 us on 8 ranks, 140 us against 152 us
+      on 2; the 36-layer prefill + decode step 31.4 ms against 35.3 ms on 8 ranks, 1-3 % faster on 2 (46.9 ms against
+      48.5 ms on one box, 48.9-49.0 ms against 49.4-49.8 ms on another), and 35.6 ms against 35.4 ms on 4, which
+      therefore keep NCCL.  ``sym_reduce = False`` or ``NQ_SYM_REDUCE=0`` keeps
+      NCCL everywhere;
     * anything else: NCCL's all-reduce, as in the reference.
 
     With ``overlap_chunks`` > 1 the GEMM runs in chunks of token rows and the exchange of chunk *i* runs on a second
@@ -221,7 +224,8 @@ class RowParallelLinear(LinearBase):
     """
 
     p2p_reduce = True            # small outputs are summed over peer memory instead of NCCL (see p2p_reduce.py)
-    sym_reduce = None            # large outputs over a peer-mapped buffer (see sym_reduce.py): None = on 8 ranks only
+    sym_reduce = None            # large outputs over a peer-mapped buffer (see sym_reduce.py): None = on 2 and 8 ranks
+    sym_auto_ranks = (2, 8)      # group sizes where that measured faster than NCCL on B200s
     overlap_chunks = 1
     overlap_min_rows = 2048      # smaller batches take one GEMM and one reduction
     overlap_chunk_rows = 1024    # a chunk is never smaller than this (and always a multiple of 128 rows)
@@ -245,7 +249,7 @@ class RowParallelLinear(LinearBase):
         if self.tp_size == 1:
             return self._linear(x, bias)
         rows = math.prod(x.shape[:-1])
-        use_sym = self.sym_reduce if self.sym_reduce is not None else self.tp_size == 8
+        use_sym = self.sym_reduce if self.sym_reduce is not None else self.tp_size in self.sym_auto_ranks
         if (use_sym and x.is_cuda and rows >= self.overlap_min_rows
                 and not torch.cuda.is_current_stream_capturing()):
             sym = sym_reduce.get_reducer()
