@@ -212,7 +212,8 @@ int nq_row_reduce_p2p(const void* partial, void* y, int64_t count,
  * Stands in for the same `dist.all_reduce(y)` (linear.py:154-155) when y is large.  The partial outputs of all
  * ranks live at the same offset of a buffer that every GPU of the group has mapped (the host obtains the
  * mappings from its symmetric-memory allocator; this library only needs the pointers).  One kernel per rank, a
- * two-shot exchange in which every transfer is a pull (16-byte loads from the peers' buffers): rank r adds slice r
+ * two-shot exchange in which every transfer is a pull (bulk asynchronous copies from the peers' buffers into
+ * shared memory; no multicast, no tensor map): rank r adds slice r
  * of all ranks' partials in rank order in fp32, writes the sum to y and back into its own buffer, and after a
  * barrier fetches the other slices' sums from their owners into y; a last barrier keeps every buffer intact until
  * all peers have read it.  All ranks end with the same bits.
@@ -221,7 +222,9 @@ int nq_row_reduce_p2p(const void* partial, void* y, int64_t count,
  *   pads   : HOST array of tp device pointers, entry r = rank r's signal pad (NQ_SYM_PAD_BYTES, zero-filled once,
  *            peer-mapped) as mapped in this process
  *   state  : 16 bytes of zero-filled device memory private to the rank (call counter; graph-replay safe)
- *   blocks : thread blocks to use, 1..NQ_SYM_MAX_BLOCKS, THE SAME ON EVERY RANK (block b pairs with block b)
+ *   blocks : thread blocks to use, 1..NQ_SYM_MAX_BLOCKS, THE SAME ON EVERY RANK (block b pairs with block b);
+ *            measured on B200s for 64 MiB: 32 blocks reach the rate of any larger count (219 us on 8 ranks, 140 us
+ *            on 2), 16 blocks 240 / 195 us
  * tp must be 2, 4 or 8.  All ranks must make the same sequence of calls.  Waits are bounded
  * (nq_set_wait_limit_ns); a peer that never arrives yields NQ_ERR_DEVICE_TIMEOUT in nq_device_status (site 80..82,
  * aux = the peer) and a wrong result. */
