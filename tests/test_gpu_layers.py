@@ -127,7 +127,7 @@ def test_cuda_graph_replay_equals_eager(L, stack06):
             assert torch.equal(outs[n].view(torch.int16), eager[n].view(torch.int16)), n
 
 
-@pytest.mark.parametrize("name,m", [("qkv", 8192), ("down", 4096), ("gate_up", 2048), ("o_proj", 256), ("gate_up", 64),
+@pytest.mark.parametrize("name,m", [("qkv", 8192), ("down", 4096), ("gate_up", 2048), ("o_proj", 256), ("gate_up", 256), ("gate_up", 64),
                                     ("gate_up", 4), ("down", 1)])
 def test_full_size_8b_layers_sampled_rows_and_linearity(L, name, m):
     """Qwen3-8B-sized layers: sampled rows against the oracle, plus size-independent properties."""
